@@ -25,6 +25,18 @@ class ConfigError(ValueError):
 _MISSING = dataclasses.MISSING
 
 
+def architecture_name(data: Any) -> str:
+    """The model class a ``config.json`` names: ``architectures[0]``, or the
+    string under ``architecture``."""
+    if isinstance(data, dict):
+        archs = data.get("architectures")
+        if isinstance(archs, list) and archs and isinstance(archs[0], str):
+            return archs[0]
+        if isinstance(data.get("architecture"), str):
+            return data["architecture"]
+    raise ConfigError("config.json lacks 'architectures': [name]")
+
+
 def _coerce(name: str, value: Any, annotation: Any) -> Any:
     """Check ``value`` against the annotation of a field (a string under
     ``from __future__ import annotations``, else the type itself)."""
@@ -80,10 +92,7 @@ class ModelConfig:
     def from_dict(cls, data: dict[str, Any]) -> "ModelConfig":
         if not isinstance(data, dict):
             raise ConfigError("config.json must hold a JSON object")
-        archs = data.get("architectures")
-        if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-            raise ConfigError("config.json lacks 'architectures': [name]")
-        values: dict[str, Any] = {"architecture": archs[0]}
+        values: dict[str, Any] = {"architecture": architecture_name(data)}
         for field in dataclasses.fields(cls):
             if field.name == "architecture":
                 continue

@@ -12,7 +12,7 @@ from __future__ import annotations
 import dataclasses
 from typing import Any, Callable, Type
 
-from .base import ConfigError, ModelConfig, read_config_json
+from .base import ConfigError, ModelConfig, architecture_name, read_config_json
 
 
 @dataclasses.dataclass(frozen=True)
@@ -56,10 +56,7 @@ def get_architecture(name: str) -> Architecture:
 
 
 def config_from_dict(data: dict) -> ModelConfig:
-    archs = data.get("architectures") if isinstance(data, dict) else None
-    if not isinstance(archs, list) or not archs:
-        raise ConfigError("config.json lacks 'architectures': [name]")
-    return get_architecture(archs[0]).config_class.from_dict(data)
+    return get_architecture(architecture_name(data)).config_class.from_dict(data)
 
 
 def load_config(folder: str) -> ModelConfig:
@@ -75,4 +72,4 @@ def _ensure_builtin() -> None:
     if _builtin_done:
         return
     _builtin_done = True
-    from ..models import qwen3  # noqa: F401  (registers itself on import)
+    from ..models import qwen3, venizen  # noqa: F401  (they register themselves on import)

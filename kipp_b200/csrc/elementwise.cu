@@ -152,3 +152,69 @@ extern "C" int kipp_rmsnorm_deferred(void* out, int out_dtype, float* ssq_out, c
     if (ssq_out == nullptr) return KIPP_ERR_ARG;
     return rmsnorm_launch(out, out_dtype, x, w, w_dtype, rows, n_rows, size, 0.f, ssq_out, stream);
 }
+
+// ---------------------------------------------------------------------------
+// PolyNorm activation over each row of z [rows, n]:
+//   y = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3,
+// powers taken element by element, N(x) = x / sqrt(mean(x^2) + eps) over the
+// row.  The three mean squares (of z, z^2 and z^3) and the polynomial are
+// float32; z arrives and y leaves in the compute type.  One block per row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+polynorm_kernel(T* __restrict__ out, long long ld_out, const T* __restrict__ z, long long ld_z,
+                const float* __restrict__ coef, int n, float eps) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* src = z + (size_t)blockIdx.x * ld_z;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = to_f32(src[i]);
+        const float v2 = v * v, v3 = v2 * v;
+        s2 += v2;
+        s4 = fmaf(v2, v2, s4);
+        s6 = fmaf(v3, v3, s6);
+    }
+    s2 = block_sum(s2, scratch);
+    s4 = block_sum(s4, scratch);
+    s6 = block_sum(s6, scratch);
+    const float inv_n = 1.0f / (float)n;
+    const float r1 = coef[0] / sqrtf(s2 * inv_n + eps), r2 = coef[1] / sqrtf(s4 * inv_n + eps);
+    const float r3 = coef[2] / sqrtf(s6 * inv_n + eps), c3 = coef[3];
+    T* dst = out + (size_t)blockIdx.x * ld_out;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = to_f32(src[i]);
+        const float v2 = v * v;
+        dst[i] = from_f32<T>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, c3))));
+    }
+}
+
+extern "C" int kipp_polynorm(void* out, long long ld_out, const void* z, long long ld_z, int dtype,
+                             const float* coef, int rows, int n, float eps, void* stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0 || coef == nullptr) return KIPP_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(polynorm_kernel<float>, dim3(rows), dim3(threads), 0, s, 1, (float*)out, ld_out,
+                           (const float*)z, ld_z, coef, n, eps);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(polynorm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, 1, (bf16*)out, ld_out,
+                           (const bf16*)z, ld_z, coef, n, eps);
+    return KIPP_ERR_DTYPE;
+}
+
+// x += y over n float32 values (the embedding output fed back into the residual stream).
+__global__ void add_f32_kernel(float* __restrict__ x, const float* __restrict__ y, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += y[i];
+}
+
+extern "C" int kipp_add_f32(float* x, const float* y, long long n, void* stream) {
+    if (n <= 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return kipp_launch(add_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, x, y, n);
+}

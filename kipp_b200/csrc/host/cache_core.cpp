@@ -10,6 +10,7 @@
 // (src/kipp.c:3616-3635 grow or leave untouched, :3755-3768 truncate, :3776-3791
 // release).  Prefix sharing (the reference's content index and reference counts) is
 // not built: a page has one owner at most.
+#include <algorithm>
 #include <cstdint>
 #include <deque>
 #include <unordered_map>
@@ -111,6 +112,7 @@ struct Request {
 struct Group {
     Pool pool;
     int window;                                      // -1: every key is kept
+    int keep_first = 0;                              // a window group never gives back positions below this
     Group(int pages, int w) : pool(pages), window(w) {}
 };
 
@@ -177,6 +179,16 @@ extern "C" void* kipp_cm_create(int n_groups, const int* n_pages, const int* win
     return m;
 }
 extern "C" void kipp_cm_destroy(void* h) { delete static_cast<Manager*>(h); }
+
+// A window group keeps the positions below keep_first for as long as the request lives (the
+// first tokens of a sequence that every later token still sees).  To be set before any request
+// is admitted.
+extern "C" int kipp_cm_set_keep_first(void* h, int group, int keep_first) {
+    Manager* m = static_cast<Manager*>(h);
+    if (group < 0 || group >= (int)m->groups.size() || keep_first < 0 || !m->requests.empty()) return ERR_ARGUMENT;
+    m->groups[(size_t)group].keep_first = keep_first;
+    return OK;
+}
 
 // The pool and the slots of a manager, for the stand-alone calls above (not to be destroyed).
 extern "C" void* kipp_cm_pool(void* h, int group) { return &static_cast<Manager*>(h)->groups[(size_t)group].pool; }
@@ -284,7 +296,9 @@ extern "C" int kipp_cm_advance(void* h, int64_t rid, int new_length) {
         std::vector<int>& table = r->tables[g];
         int keep_from = m->first_needed_position(grp, new_length) / m->page_size;
         if (keep_from > (int)table.size()) keep_from = (int)table.size();
-        for (int lp = r->first_live[g]; lp < keep_from; ++lp)
+        // pages that hold a kept position stay, however far the window has moved on
+        const int kept_pages = grp.keep_first > 0 ? (grp.keep_first + m->page_size - 1) / m->page_size : 0;
+        for (int lp = std::max(r->first_live[g], kept_pages); lp < keep_from; ++lp)
             if (table[(size_t)lp] != UNMAPPED) {
                 const int rc = grp.pool.release(table[(size_t)lp], rid);
                 if (rc) return rc;

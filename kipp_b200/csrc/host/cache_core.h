@@ -16,6 +16,7 @@ extern "C" {
 
 void* kipp_cm_create(int n_groups, const int* n_pages, const int* windows, int page_size, int max_requests);
 void kipp_cm_destroy(void* h);
+int kipp_cm_set_keep_first(void* h, int group, int keep_first);
 void* kipp_cm_pool(void* h, int group);
 void* kipp_cm_slots(void* h);
 int kipp_pool_free_pages(void* pool);

@@ -13,7 +13,9 @@
 
 #include "cache_core.h"
 #include "parts.hpp"
+#include "recurrent_parts.hpp"
 #include "qwen3.hpp"
+#include "venizen.hpp"
 
 namespace kipp {
 
@@ -76,7 +78,7 @@ public:
                 if (!s.optional) missing.push_back(s.name);
                 continue;
             }
-            if (t.shape != s.shape)
+            if (!shape_fits(t.shape, s.shape))
                 lines.push_back("  wrong shape: " + s.name + " is " + shape_text(t.shape) + ", expected " +
                                 shape_text(s.shape));
             if (t.dtype < 0 || t.dtype > U8) lines.push_back("  unsupported dtype: " + s.name);
@@ -200,6 +202,7 @@ public:
     int groups() const { return (int)groups_.size(); }
     int group_pages(int g) const { return groups_[(size_t)g].n_pages; }
     int group_window(int g) const { return groups_[(size_t)g].spec.window; }
+    int group_keep_first(int g) const { return groups_[(size_t)g].spec.window > 0 ? groups_[(size_t)g].spec.keep_first : 0; }
     int group_free_pages(int g) const { return kipp_pool_free_pages(kipp_cm_pool(cm_, g)); }
     int free_slots() const { return kipp_slots_free_count(kipp_cm_slots(cm_)); }
     cudaStream_t stream() const { return stream_; }
@@ -217,8 +220,9 @@ private:
         PagedKVSpec spec;
         std::vector<long long> cache_keys;    // (cache id, mixer slot) of the runs that share these pools, in storage order
         int n_pages = 0;
-        DeviceBuffer k, v;                    // [caches, pages, kv_heads, page_size, head_dim]
-        size_t cache_stride = 0;              // bytes between two caches of the group
+        DeviceBuffer k, v;                    // [caches, pages, kv_heads, page_size, head_dim (values: value dim)]
+        size_t cache_stride = 0;              // bytes between two caches of the group's keys
+        size_t value_stride = 0;              // ... and of its values
     };
     struct StateBuffer {
         StateSpec spec;
@@ -311,32 +315,37 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
     const size_t es = ctx.element();
     Ops& ops = *ctx.ops;
     const StepMeta& m = *ctx.meta;
-    const int qkv_cols = q_dim_ + 2 * kv_dim_;
+    const int qkv_cols = q_dim_ + kv_dim_ + vv_dim_;
     NormFold fold_in, fold_out;
     const PagedCacheView cache = ctx.cache_view(run, mixer_slot);       // pages of this run's cache id
     const int rot = position_->rotary_dim();
-    const bool to_heads = ctx.dtype == dtype_ && !ctx.kv_round_bf16 &&
+    const bool to_heads = !mix_path_ && ctx.dtype == dtype_ && !ctx.kv_round_bf16 &&
                           Ops::projection_to_heads_ok(dtype_, h, hidden_, w_qkv_, hidden_, T, head_dim_, rot);
-    const float* cos_sin = nullptr;
-    if (rot > 0) {
-        // the step's (cos, sin) table: the same for every layer that rotates alike; laid out by
-        // pair for the projection that rotates its own heads
-        const std::string key = (to_heads ? "rope by pair/" : "rope/") + position_->table_key();
-        auto it = ctx.step_cache.find(key);
-        if (it == ctx.step_cache.end()) {
-            int made = 0;
-            for (auto& kv : ctx.step_cache) made += kv.first.rfind("rope", 0) == 0;
-            float* table = ctx.workspace->get<float>("rope_table_" + std::to_string(made), (size_t)T * rot);
-            if (to_heads) ops.rope_table_by_pair(table, m.positions, position_->inv_freq_device(), T, rot / 2);
-            else ops.rope_table(table, m.positions, position_->inv_freq_device(), T, rot / 2);
-            it = ctx.step_cache.emplace(key, table).first;
-        }
-        cos_sin = static_cast<const float*>(it->second);
-    }
-    void* attn = ctx.workspace->buffer("attn_out", (size_t)T * q_dim_ * es);
-    const AttentionWork work = planner_->work_of(m);
+    // the step's (cos, sin) table: the same for every layer that rotates alike; laid out by
+    // pair for the projection that rotates its own heads
+    const float* cos_sin = step_rope_table(ctx, *position_, to_heads);
+    void* attn = ctx.workspace->buffer("attn_out", (size_t)T * o_dim_ * es);
     const void* qn = qk_norm_ ? q_norm_ : nullptr;
     const void* kn = qk_norm_ ? k_norm_ : nullptr;
+    if (mix_path_) {
+        // mixed heads, kept first tokens, value heads of their own size or a scaled output: every
+        // head of a query is handled together, scores and weights in float32
+        void* qkv = ctx.workspace->buffer("qkv", (size_t)T * qkv_cols * es);
+        ops.gemm(qkv, ctx.dtype, qkv_cols, h, hidden_, w_qkv_, hidden_, dtype_, T, qkv_cols, hidden_, EPI_STORE,
+                 fold_input(ctx, fold_in));
+        void* q = ctx.workspace->buffer("q", (size_t)T * q_dim_ * es);
+        const int write = (run.writes_cache ? 1 : 0) | (ctx.kv_round_bf16 && ctx.dtype == F32 ? 2 : 0);
+        ops.qk_norm_rope_write(qkv, qkv_cols, q, cache, ctx.dtype, qn, kn, norm_dtype_, eps_, cos_sin, rot, m.positions,
+                               m.entry_of_token, T, heads_, kv_heads_, head_dim_, write, v_dim_);
+        ops.attention_mix(attn, q, cache, ctx.dtype, head_mix_, m.positions, m.entry_of_token, T, heads_, kv_heads_,
+                          head_dim_, v_dim_, scale_, window_, window_ > 0 ? opt_.keep_first : 0,
+                          (float)opt_.output_scale);
+        const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
+        ops.gemm(residual, F32, hidden_, attn, o_dim_, w_o_, o_dim_, dtype_, T, hidden_, o_dim_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
+        return;
+    }
+    const AttentionWork work = planner_->work_of(m);
     if (to_heads) {
         // a prompt-sized step: the projection's epilogue norms, rotates and writes the cache
         void* q = ctx.workspace->buffer("q", (size_t)T * q_dim_ * es);
@@ -379,6 +388,7 @@ public:
         return source_.get(name, t);
     }
     int stored_dtype(const std::string& name) override { return fetch(name).dtype; }
+    std::vector<int64_t> stored_shape(const std::string& name) override { return fetch(name).shape; }
     void* allocate(size_t bytes, const std::string& what) override {
         e_.weight_memory_.emplace_back(bytes, what.c_str());
         e_.weight_bytes_allocated_ += bytes;
@@ -510,7 +520,7 @@ inline void Engine::check_memory(const std::vector<TensorSpec>& specs) {
     for (auto& s : specs) {
         if (s.optional && !s.alias_of.empty()) continue;
         size_t n = es;
-        for (auto d : s.shape) n *= (size_t)d;
+        for (auto d : s.shape) n *= (size_t)(d > 0 ? d : 1);      // a size left open counts as 1
         weights += n;
     }
     size_t per_token = 0;
@@ -519,7 +529,7 @@ inline void Engine::check_memory(const std::vector<TensorSpec>& specs) {
         auto mixers = plan_->layers[(size_t)run.layer].second->mixers();
         for (size_t s = 0; s < mixers.size(); ++s)
             if (auto cs = mixers[s]->cache_spec(); cs && seen.insert(cache_key(run.cache, (int)s)).second)
-                per_token += (size_t)2 * cs->kv_heads * cs->head_dim * es;
+                per_token += (size_t)cs->kv_heads * (cs->head_dim + cs->v_dim()) * es;
     }
     size_t free_bytes = 0, total = 0;
     cuda_check(cudaMemGetInfo(&free_bytes, &total), "cudaMemGetInfo");
@@ -589,11 +599,12 @@ inline void Engine::build_cache() {
         g.cache_keys = by_spec[spec];
         g.n_pages = n_pages;
         g.cache_stride = (size_t)n_pages * spec.kv_heads * opt_.page_size * spec.head_dim * es;
-        const size_t bytes = g.cache_stride * g.cache_keys.size();
+        g.value_stride = (size_t)n_pages * spec.kv_heads * opt_.page_size * spec.v_dim() * es;
+        const size_t bytes = g.cache_stride * g.cache_keys.size(), value_bytes = g.value_stride * g.cache_keys.size();
         g.k.reset(bytes, "key pages");
-        g.v.reset(bytes, "value pages");
+        g.v.reset(value_bytes, "value pages");
         cuda_check(cudaMemsetAsync(g.k.get(), 0, bytes, stream_), "clearing the key pages");
-        cuda_check(cudaMemsetAsync(g.v.get(), 0, bytes, stream_), "clearing the value pages");
+        cuda_check(cudaMemsetAsync(g.v.get(), 0, value_bytes, stream_), "clearing the value pages");
         for (size_t j = 0; j < g.cache_keys.size(); ++j)
             group_of_cache_[g.cache_keys[j]] = {(int)groups_.size() - 1, (int)j};
         pages.push_back(n_pages);
@@ -603,6 +614,9 @@ inline void Engine::build_cache() {
     cm_ = kipp_cm_create((int)groups_.size(), pages.empty() ? &dummy : pages.data(),
                          windows.empty() ? &dummy : windows.data(), opt_.page_size, opt_.max_requests);
     if (!cm_) fail(KIPP_E_ARGUMENT, "the cache manager could not be created");
+    for (size_t g = 0; g < groups_.size(); ++g)
+        if (groups_[g].spec.window > 0 && groups_[g].spec.keep_first > 0)
+            kipp_cm_set_keep_first(cm_, (int)g, groups_[g].spec.keep_first);
     for (auto& kv : state_specs) {
         StateBuffer& sb = states_[kv.first];
         sb.spec = kv.second;
@@ -619,7 +633,7 @@ inline PagedCacheView Engine::cache_view(const StepMeta& meta, const LayerRun& r
     const CacheGroup& g = groups_[(size_t)it->second.first];
     PagedCacheView v;
     v.k_pages = static_cast<char*>(g.k.get()) + g.cache_stride * (size_t)it->second.second;
-    v.v_pages = static_cast<char*>(g.v.get()) + g.cache_stride * (size_t)it->second.second;
+    v.v_pages = static_cast<char*>(g.v.get()) + g.value_stride * (size_t)it->second.second;
     v.n_pages = g.n_pages;
     v.block_table = meta.block_tables[(size_t)it->second.first];
     v.table_width = meta.table_widths[(size_t)it->second.first];
@@ -829,13 +843,22 @@ inline const float* Engine::forward(StepMeta& meta) {
     const int T = meta.shape.tokens;
     float* x = workspace_.get<float>("residual", (size_t)T * plan_->hidden_size);
     for (auto& e : plan_->embedding) e.second->forward(ctx, x);
+    // a run that adds the embedding output to the stream needs it kept
+    float* embedded = nullptr;
+    for (auto& run : plan_->order)
+        if (run.adds_embedding && embedded == nullptr) {
+            embedded = workspace_.get<float>("embedding_output", (size_t)T * plan_->hidden_size);
+            cuda_check(cudaMemcpyAsync(embedded, x, (size_t)T * plan_->hidden_size * sizeof(float),
+                                       cudaMemcpyDeviceToDevice, stream_), "keeping the embedding output");
+        }
     for (size_t i = 0; i < plan_->order.size(); ++i) {
         const LayerRun& run = plan_->order[i];
+        if (run.adds_embedding) ops_.add_f32(x, embedded, (long long)T * plan_->hidden_size);
         // the block that runs next starts with this norm: the last residual add of this one may
-        // leave its deferred form
-        ctx.following_norm = i + 1 < plan_->order.size()
-                                 ? plan_->layers[(size_t)plan_->order[i + 1].layer].second->deferred_first_norm()
-                                 : nullptr;
+        // leave its deferred form, unless something is added to the stream in between
+        const bool next_plain = i + 1 < plan_->order.size() && !plan_->order[i + 1].adds_embedding;
+        ctx.following_norm = next_plain ? plan_->layers[(size_t)plan_->order[i + 1].layer].second->deferred_first_norm()
+                                        : nullptr;
         plan_->layers[(size_t)run.layer].second->forward(ctx, run, x);
     }
     const float* logits = nullptr;
@@ -1330,7 +1353,7 @@ inline size_t Engine::weight_bytes() const {
 inline size_t Engine::cache_bytes_per_token() const {
     size_t n = 0;
     for (auto& g : groups_)
-        n += (size_t)2 * g.cache_keys.size() * g.spec.kv_heads * g.spec.head_dim * dtype_size(dtype_);
+        n += g.cache_keys.size() * g.spec.kv_heads * (g.spec.head_dim + g.spec.v_dim()) * dtype_size(dtype_);
     return n;
 }
 
@@ -1338,7 +1361,7 @@ inline size_t Engine::cache_bytes_per_token() const {
 // one, src/kipp.h:109-145, 172-200).
 inline std::string Engine::info_json() {
     Json j = Json::object();
-    if (plan_->config.is_object() && plan_->config.has("architectures"))
+    if (plan_->config.is_object() && (plan_->config.has("architectures") || plan_->config.has("architecture")))
         j.set("architecture", architecture_of(plan_->config));
     j.set("dtype", dtype_name(dtype_));
     j.set("device", opt_.device);
@@ -1367,7 +1390,9 @@ inline std::string Engine::info_json() {
         o.set("caches", (long long)groups_[g].cache_keys.size());
         o.set("kv_heads", groups_[g].spec.kv_heads);
         o.set("head_dim", groups_[g].spec.head_dim);
+        o.set("value_dim", groups_[g].spec.v_dim());
         o.set("window", groups_[g].spec.window > 0 ? Json(groups_[g].spec.window) : Json(nullptr));
+        o.set("keep_first", groups_[g].spec.window > 0 ? groups_[g].spec.keep_first : 0);
         o.set("pages", groups_[g].n_pages);
         o.set("free_pages", group_free_pages((int)g));
         groups.push(std::move(o));

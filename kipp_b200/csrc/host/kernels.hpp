@@ -202,14 +202,82 @@ public:
     void qk_norm_rope_write(const void* qkv, int ld_qkv, void* q_out, const PagedCacheView& cache, int dtype,
                             const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps, const float* cos_sin,
                             int rotary_dim, const int* positions, const int* entry_of_token, int tokens, int n_q,
-                            int n_kv, int head_dim, int write_cache) {
+                            int n_kv, int head_dim, int write_cache, int value_dim = 0) {
         using Fn = int (*)(const void*, int, void*, void*, void*, int, const void*, const void*, int, float, const void*,
-                           int, const int*, const int*, const int*, int, int, int, int, int, int, int, int*, void*);
-        static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_qk_norm_rope_write");
+                           int, const int*, const int*, const int*, int, int, int, int, int, int, int, int, int*, void*);
+        static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_qk_norm_rope_write_v");
         run(f(qkv, ld_qkv, q_out, cache.k_pages, cache.v_pages, dtype, q_norm_w, k_norm_w, norm_dtype, eps, cos_sin,
               cos_sin ? rotary_dim : 0, positions, entry_of_token, cache.block_table, cache.table_width,
-              cache.page_size, tokens, n_q, n_kv, head_dim, write_cache, status, stream),
+              cache.page_size, tokens, n_q, n_kv, head_dim, value_dim > 0 ? value_dim : head_dim, write_cache, status,
+              stream),
             "qk_norm_rope_write");
+    }
+
+    // Attention whose heads' scores are mixed before the softmax (head_mix [n_q, n_q] float32, or
+    // null), with a window that keeps the first keep_first positions and value heads of v_dim;
+    // the result is scaled by out_scale.  Scores, mix, softmax and weighted sum in float32.
+    void attention_mix(void* out, const void* q, const PagedCacheView& cache, int dtype, const float* head_mix,
+                       const int* positions, const int* entry_of_token, int tokens, int n_q, int n_kv, int head_dim,
+                       int v_dim, float scale, int window, int keep_first, float out_scale) {
+        using Fn = int (*)(void*, const void*, const void*, const void*, int, const float*, const int*, const int*,
+                           const int*, int, int, int, int, int, int, int, float, int, int, float, int*, void*);
+        static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix");
+        run(f(out, q, cache.k_pages, cache.v_pages, dtype, head_mix, positions, entry_of_token, cache.block_table,
+              cache.table_width, cache.page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
+              out_scale, status, stream),
+            "attention_mix");
+    }
+
+    // Whether the recurrent scan kernels take heads of these sizes.
+    static bool recurrent_scan_ok(int dim, int v_dim, bool delta) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
+        return f(dim, v_dim, delta ? 1 : 0) != 0;
+    }
+    // S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t over each entry's tokens, from the state in
+    // its slot and back into it; q and k rotated by the step's table and k scaled; then per-head
+    // root-mean-square division, gate (1 silu, 2 sigmoid of the g columns), out_scale.
+    void retention_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int q_off,
+                        int k_off, int v_off, int g_off, float* state, const float* decay, const float* cos_sin,
+                        int rot, const int* q_start, const int* slots, int entries, int heads, int dim, int v_dim,
+                        float k_scale, float eps, float out_scale, int gate) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, float*, const float*,
+                           const float*, int, const int*, const int*, int, int, int, int, float, float, float, int, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_retention_scan");
+        run(f(out, ld_out, proj, ld_proj, dtype, q_off, k_off, v_off, g_off, state, decay, cos_sin, rot, q_start, slots,
+              entries, heads, dim, v_dim, k_scale, eps, out_scale, gate, stream),
+            "retention_scan");
+    }
+    // S_t = diag(w_t) S_{t-1} - (a_t u_t)(u_t^T S_{t-1}) + k_t v_t^T, o_t = S_t^T r_t (see recurrent.cu).
+    void delta_rule_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int r_off,
+                         int k_off, int v_off, int g_off, int a_off, const void* w_raw, long long ld_w,
+                         const float* a_bias, const float* w_bias, const float* norm_w, float* state,
+                         const int* q_start, const int* slots, int entries, int heads, int dim, float eps,
+                         float out_scale, int gate) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, int, const void*, long long,
+                           const float*, const float*, const float*, float*, const int*, const int*, int, int, int,
+                           float, float, int, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_delta_rule_scan");
+        run(f(out, ld_out, proj, ld_proj, dtype, r_off, k_off, v_off, g_off, a_off, w_raw, ld_w, a_bias, w_bias, norm_w,
+              state, q_start, slots, entries, heads, dim, eps, out_scale, gate, stream),
+            "delta_rule_scan");
+    }
+    void tanh_rows(void* out, long long ld_out, const void* in, long long ld_in, int dtype, int rows, int cols) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_tanh_rows");
+        run(f(out, ld_out, in, ld_in, dtype, rows, cols, stream), "tanh_rows");
+    }
+    // y = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 per row, N = division by the row's root mean square.
+    void polynorm(void* out, long long ld_out, const void* z, long long ld_z, int dtype, const float* coef, int rows,
+                  int n, float eps) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, const float*, int, int, float, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_polynorm");
+        run(f(out, ld_out, z, ld_z, dtype, coef, rows, n, eps, stream), "polynorm");
+    }
+    void add_f32(float* x, const float* y, long long n) {
+        using Fn = int (*)(float*, const float*, long long, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_add_f32");
+        run(f(x, y, n, stream), "add_f32");
     }
 
     static bool attention_mma_supported(int head_dim, int n_q, int n_kv) {

@@ -29,19 +29,22 @@ struct LayerRun {
     int layer = 0;
     int cache = 0;
     bool writes_cache = true;
+    // the output of the embedding stages is added to the residual stream right before this run
+    // (a model that runs a span of its layers several times feeds its input in again each time)
+    bool adds_embedding = false;
 };
 
-// Cache need of a mixer: keys and values of kv_heads heads of head_dim per token.  window 0
-// keeps every key; a window of w keeps keys j with pos - w < j <= pos.  Runs with equal
-// specs share a group of the cache manager (own pool, own block tables, own retention).
+// Cache need of a mixer: keys of kv_heads heads of head_dim per token and values of
+// value_dim (0: as the keys).  window 0 keeps every key; a window of w keeps keys j with
+// pos - w < j <= pos and, beside them, the first keep_first positions of the sequence.  Runs
+// with equal specs share a group of the cache manager (own pool, own block tables, own
+// retention).
 struct PagedKVSpec {
-    int kv_heads = 0, head_dim = 0, window = 0;
-    bool operator==(const PagedKVSpec& o) const {
-        return kv_heads == o.kv_heads && head_dim == o.head_dim && window == o.window;
-    }
-    bool operator<(const PagedKVSpec& o) const {
-        return std::tie(kv_heads, head_dim, window) < std::tie(o.kv_heads, o.head_dim, o.window);
-    }
+    int kv_heads = 0, head_dim = 0, window = 0, value_dim = 0, keep_first = 0;
+    int v_dim() const { return value_dim > 0 ? value_dim : head_dim; }
+    auto key() const { return std::make_tuple(kv_heads, head_dim, window, v_dim(), window > 0 ? keep_first : 0); }
+    bool operator==(const PagedKVSpec& o) const { return key() == o.key(); }
+    bool operator<(const PagedKVSpec& o) const { return key() < o.key(); }
 };
 
 // Fixed-size per-request state of a mixer: one tensor per request, zeroed on admission.
@@ -161,6 +164,7 @@ public:
     virtual int compute_dtype() const = 0;
     virtual bool has(const std::string& name) = 0;
     virtual int stored_dtype(const std::string& name) = 0;          // DType in the checkpoint
+    virtual std::vector<int64_t> stored_shape(const std::string& name) = 0;   // for a size a spec left open (-1)
     virtual void* allocate(size_t bytes, const std::string& what) = 0;   // device memory that lives with the engine
     // dst[r * dst_pitch + c] = convert(tensor viewed as [rows, cols]); pitch in elements
     virtual void load(const std::string& name, void* dst, int dst_dtype, int64_t dst_pitch, int64_t rows,
@@ -211,6 +215,9 @@ public:
     // true: the part applies ctx.input_scale to its first product, at every size of step, and may
     // honour ctx.emit_for in its residual add
     virtual bool folds_rms() const { return false; }
+    // the mixers this one is made of, each with a cache or state of its own (mixer slot = index);
+    // a plain mixer is its own only part
+    virtual std::vector<Mixer*> parts() { return {this}; }
 };
 
 class FeedForward : public Part {
@@ -337,8 +344,8 @@ private:
     std::map<std::string, Architecture> archs_;
 };
 
-void register_builtin_parts();           // parts.hpp
-void register_builtin_architectures();   // qwen3.hpp
+void register_builtin_parts();           // parts.hpp, recurrent_parts.hpp
+void register_builtin_architectures();   // qwen3.hpp, venizen.hpp
 
 inline void ensure_registered() {
     static std::once_flag once;
@@ -348,11 +355,13 @@ inline void ensure_registered() {
     });
 }
 
+// The name a config.json gives its model class: 'architectures': [name], or 'architecture': name.
 inline std::string architecture_of(const Json& config) {
     const Json* archs = config.is_object() ? config.find("architectures") : nullptr;
-    if (!archs || !archs->is_array() || archs->size() == 0 || !archs->at(0).is_string())
-        fail(KIPP_E_CONFIG, "config.json lacks 'architectures': [name]");
-    return archs->at(0).as_string();
+    if (archs && archs->is_array() && archs->size() > 0 && archs->at(0).is_string()) return archs->at(0).as_string();
+    const Json* one = config.is_object() ? config.find("architecture") : nullptr;
+    if (one && one->is_string()) return one->as_string();
+    fail(KIPP_E_CONFIG, "config.json lacks 'architectures': [name]");
 }
 
 // Builds the parts a plan (JSON) names.
@@ -376,6 +385,7 @@ inline std::unique_ptr<ModelPlan> build_plan(const Json& j, const BuildContext& 
             run.layer = (int)r.get("layer").as_int();
             run.cache = (int)r.get_int("cache", run.layer);
             run.writes_cache = r.get_bool("writes_cache", true);
+            run.adds_embedding = r.get_bool("adds_embedding", false);
             if (run.layer < 0 || run.layer >= (int)plan->layers.size())
                 fail(KIPP_E_CONFIG, "the run order names layer " + std::to_string(run.layer) + ", which the plan lacks");
             if (run.cache < 0) fail(KIPP_E_CONFIG, "cache ids must not be negative");

@@ -11,18 +11,19 @@ namespace kipp {
 // x_t = float(E[id_t, :]) with no scale (src/kipp.c:2940-2942).
 class TokenEmbedding : public EmbeddingStage {
 public:
-    TokenEmbedding(int vocab, int hidden) : vocab_(vocab), hidden_(hidden) {
+    TokenEmbedding(int vocab, int hidden, std::string weight_name = "weight")
+        : vocab_(vocab), hidden_(hidden), name_(std::move(weight_name)) {
         if (vocab <= 0 || hidden <= 0) fail(KIPP_E_CONFIG, "token_embedding: sizes must be positive");
     }
     void tensor_specs(const std::string& prefix, std::vector<TensorSpec>& out) const override {
         TensorSpec s;
-        s.name = prefix + "weight";
+        s.name = prefix + name_;
         s.shape = {vocab_, hidden_};
         out.push_back(s);
     }
     void bind(Binder& b, const std::string& prefix) override {
         dtype_ = b.compute_dtype();
-        weight_ = b.shared(prefix + "weight", dtype_, vocab_, hidden_);
+        weight_ = b.shared(prefix + name_, dtype_, vocab_, hidden_);
     }
     void forward(StepContext& ctx, float* x) override {
         ctx.ops->embed_gather(x, weight_, dtype_, ctx.meta->token_ids, ctx.tokens(), hidden_, vocab_);
@@ -30,6 +31,7 @@ public:
 
 private:
     int vocab_, hidden_, dtype_ = BF16;
+    std::string name_;
     void* weight_ = nullptr;
 };
 
@@ -37,12 +39,13 @@ private:
 // head of its own (src/kipp.c:951-956, 3013-3018).
 class OutputHead : public Head {
 public:
-    OutputHead(int vocab, int hidden, std::string tied_to) : vocab_(vocab), hidden_(hidden), tied_to_(std::move(tied_to)) {
+    OutputHead(int vocab, int hidden, std::string tied_to, std::string weight_name = "weight")
+        : vocab_(vocab), hidden_(hidden), tied_to_(std::move(tied_to)), name_(std::move(weight_name)) {
         if (vocab <= 0 || hidden <= 0) fail(KIPP_E_CONFIG, "output_head: sizes must be positive");
     }
     void tensor_specs(const std::string& prefix, std::vector<TensorSpec>& out) const override {
         TensorSpec s;
-        s.name = prefix + "weight";
+        s.name = prefix + name_;
         s.shape = {vocab_, hidden_};
         if (!tied_to_.empty()) {
             s.optional = true;
@@ -53,7 +56,7 @@ public:
     }
     void bind(Binder& b, const std::string& prefix) override {
         dtype_ = b.compute_dtype();
-        weight_ = b.shared(tied_to_.empty() ? prefix + "weight" : tied_to_, dtype_, vocab_, hidden_);
+        weight_ = b.shared(tied_to_.empty() ? prefix + name_ : tied_to_, dtype_, vocab_, hidden_);
     }
     size_t weight_bytes() const override { return (size_t)vocab_ * hidden_ * dtype_size(dtype_); }
     int vocab_size() const override { return vocab_; }
@@ -63,7 +66,7 @@ public:
 
 private:
     int vocab_, hidden_, dtype_ = BF16;
-    std::string tied_to_;
+    std::string tied_to_, name_;
     void* weight_ = nullptr;
 };
 
@@ -127,12 +130,14 @@ private:
 // Half-split rotary encoding (src/kipp.c:2368-2382): the frequency of pair i is
 // theta^(-2i/rot) as the reference's powf(theta, -(2.0f * i) / rot): a float32 exponent, the
 // power rounded to float32 once.
-inline std::vector<float> rotary_frequencies(int rotary_dim, double theta) {
+// `exact`: the exponent -2i/rot in double precision instead (the power still rounded to float32
+// once), for models whose frequencies are defined as the real number theta^(-2i/rot).
+inline std::vector<float> rotary_frequencies(int rotary_dim, double theta, bool exact = false) {
     std::vector<float> f((size_t)rotary_dim / 2);
-    const double base = (double)(float)theta;
+    const double base = exact ? theta : (double)(float)theta;
     for (int i = 0; i < rotary_dim / 2; ++i) {
         const float exponent = -(2.0f * (float)i) / (float)rotary_dim;
-        f[(size_t)i] = (float)std::pow(base, (double)exponent);
+        f[(size_t)i] = (float)std::pow(base, exact ? -2.0 * (double)i / (double)rotary_dim : (double)exponent);
     }
     return f;
 }
@@ -322,48 +327,103 @@ inline void fold_emitted(StepContext& ctx, const NormFold* f, int hidden) {
     ctx.emitted_scale = RowScale{f->ssq_out, hidden / 32, 1.0f / (float)hidden, ctx.emit_for->eps};
 }
 
+// The step's (cos, sin) table of a position encoding: made once per forward pass and shared by
+// every part that rotates alike (by token, or laid out by pair for the projection that rotates
+// its own heads).
+inline const float* step_rope_table(StepContext& ctx, const PositionEncoding& position, bool by_pair) {
+    const int rot = position.rotary_dim(), T = ctx.tokens();
+    if (rot <= 0) return nullptr;
+    const std::string key = (by_pair ? "rope by pair/" : "rope/") + position.table_key();
+    auto it = ctx.step_cache.find(key);
+    if (it == ctx.step_cache.end()) {
+        int made = 0;
+        for (auto& kv : ctx.step_cache) made += kv.first.rfind("rope", 0) == 0;
+        float* table = ctx.workspace->get<float>("rope_table_" + std::to_string(made), (size_t)T * rot);
+        if (by_pair) ctx.ops->rope_table_by_pair(table, ctx.meta->positions, position.inv_freq_device(), T, rot / 2);
+        else ctx.ops->rope_table(table, ctx.meta->positions, position.inv_freq_device(), T, rot / 2);
+        it = ctx.step_cache.emplace(key, table).first;
+    }
+    return static_cast<const float*>(it->second);
+}
+
+// Names of a part's checkpoint tensors under its prefix: the defaults, or what the plan gives.
+inline std::map<std::string, std::string> tensor_names(const Json& j, std::map<std::string, std::string> defaults) {
+    if (const Json* n = j.find("names"); n && n->is_object())
+        for (auto& kv : n->members()) {
+            if (!defaults.count(kv.first)) fail(KIPP_E_CONFIG, "unknown tensor role '" + kv.first + "' in 'names'");
+            defaults[kv.first] = kv.second.as_string();
+        }
+    return defaults;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Causal grouped-query attention over the paged cache, with optional per-head q/k RMSNorm and a
 // position encoding applied to q and k.  Order of operations as the reference's block
 // (docs/ARCHITECTURE.md:77-92, src/kipp.c:2950-2993): q/k/v projections (no bias) -> per-head
 // norm of q and k -> rotation -> keys and values into the cache -> attention -> output
 // projection added to the residual stream.
+//
+// Options beyond that (each off by default): value heads of a size of their own (value_dim); a
+// window that keeps the first keep_first positions of the sequence visible; a matrix that mixes
+// the heads' scores before the softmax (head_mix: score_h <- sum_g M[h][g] score_g, a tensor
+// [heads, heads]); a factor on the mixer's output (output_scale).  With any of them the step runs
+// on the attention_mix kernel, which holds all heads of a query together.
+struct AttentionOptions {
+    int value_dim = 0, keep_first = 0;
+    bool head_mix = false;
+    double output_scale = 1.0;
+    std::map<std::string, std::string> names = {{"q", "q_proj.weight"}, {"k", "k_proj.weight"}, {"v", "v_proj.weight"},
+                                                {"o", "o_proj.weight"}, {"q_norm", "q_norm.weight"},
+                                                {"k_norm", "k_norm.weight"}, {"head_mix", "head_mix.weight"}};
+};
+
 class AttentionMixer : public Mixer {
 public:
     AttentionMixer(int hidden, int heads, int kv_heads, int head_dim, std::unique_ptr<PositionEncoding> position,
-                   std::optional<double> qk_norm_eps, int window, std::optional<double> scale)
+                   std::optional<double> qk_norm_eps, int window, std::optional<double> scale,
+                   AttentionOptions options = {})
         : hidden_(hidden), heads_(heads), kv_heads_(kv_heads), head_dim_(head_dim), position_(std::move(position)),
-          qk_norm_(qk_norm_eps.has_value()), eps_(qk_norm_eps ? (float)*qk_norm_eps : 0.f), window_(window) {
+          qk_norm_(qk_norm_eps.has_value()), eps_(qk_norm_eps ? (float)*qk_norm_eps : 0.f), window_(window),
+          opt_(std::move(options)) {
         if (hidden <= 0 || heads <= 0 || kv_heads <= 0 || head_dim <= 0)
             fail(KIPP_E_CONFIG, "attention: sizes must be positive");
         if (heads % kv_heads) fail(KIPP_E_CONFIG, "attention: num_heads must be a multiple of num_kv_heads");
         if (window < 0) fail(KIPP_E_CONFIG, "attention: a window must not be negative");
+        if (opt_.value_dim < 0 || opt_.keep_first < 0) fail(KIPP_E_CONFIG, "attention: value_dim and keep_first must not be negative");
         if (position_->rotary_dim() > head_dim || position_->rotary_dim() % 2)
             fail(KIPP_E_CONFIG, "attention: rotary_dim must be even and at most head_dim");
         scale_ = scale ? (float)*scale : (float)(1.0 / std::sqrt((double)head_dim));
+        v_dim_ = opt_.value_dim > 0 ? opt_.value_dim : head_dim;
         q_dim_ = heads * head_dim;
         kv_dim_ = kv_heads * head_dim;
+        vv_dim_ = kv_heads * v_dim_;
+        o_dim_ = heads * v_dim_;
+        mix_path_ = opt_.head_mix || (window_ > 0 && opt_.keep_first > 0) || v_dim_ != head_dim_ || opt_.output_scale != 1.0;
     }
     void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
-        auto add = [&](const char* n, std::vector<int64_t> shape, const char* init = "normal") {
+        auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
             TensorSpec s;
-            s.name = p + n;
+            s.name = p + opt_.names.at(role);
             s.shape = std::move(shape);
             s.init = init;
             out.push_back(s);
         };
-        add("q_proj.weight", {q_dim_, hidden_});
-        add("k_proj.weight", {kv_dim_, hidden_});
-        add("v_proj.weight", {kv_dim_, hidden_});
-        add("o_proj.weight", {hidden_, q_dim_});
+        add("q", {q_dim_, hidden_});
+        add("k", {kv_dim_, hidden_});
+        add("v", {vv_dim_, hidden_});
+        add("o", {hidden_, o_dim_});
         if (qk_norm_) {
-            add("q_norm.weight", {head_dim_}, "near_one");
-            add("k_norm.weight", {head_dim_}, "near_one");
+            add("q_norm", {head_dim_}, "near_one");
+            add("k_norm", {head_dim_}, "near_one");
         }
+        if (opt_.head_mix) add("head_mix", {heads_, heads_}, "near_identity");
         position_->tensor_specs(p, out);
     }
-    std::optional<PagedKVSpec> cache_spec() const override { return PagedKVSpec{kv_heads_, head_dim_, window_}; }
+    std::optional<PagedKVSpec> cache_spec() const override {
+        return PagedKVSpec{kv_heads_, head_dim_, window_, v_dim_, window_ > 0 ? opt_.keep_first : 0};
+    }
     std::shared_ptr<WorkPlanner> planner(const DeviceInfo& dev, bool own_length) override {
+        if (mix_path_) return nullptr;            // the attention_mix kernel reads the common metadata only
         auto p = std::make_shared<AttentionPlanner>(kv_heads_, dev.sm_count, own_length);
         planner_ = p;
         return p;
@@ -371,30 +431,38 @@ public:
     void bind(Binder& b, const std::string& p) override {
         dtype_ = b.compute_dtype();
         const size_t es = dtype_size(dtype_);
-        const int64_t rows = q_dim_ + 2 * kv_dim_;
+        const int64_t rows = q_dim_ + kv_dim_ + vv_dim_;
+        const std::string nq = p + opt_.names.at("q"), nk = p + opt_.names.at("k"), nv = p + opt_.names.at("v");
+        const std::string no = p + opt_.names.at("o");
         // one matrix for q, k and v so that one product makes all three
         w_qkv_ = b.allocate((size_t)rows * hidden_ * es, p + "qkv");
         char* base = static_cast<char*>(w_qkv_);
-        b.load(p + "q_proj.weight", base, dtype_, hidden_, q_dim_, hidden_);
-        b.load(p + "k_proj.weight", base + (size_t)q_dim_ * hidden_ * es, dtype_, hidden_, kv_dim_, hidden_);
-        b.load(p + "v_proj.weight", base + (size_t)(q_dim_ + kv_dim_) * hidden_ * es, dtype_, hidden_, kv_dim_,
-               hidden_);
-        w_o_ = b.allocate((size_t)hidden_ * q_dim_ * es, p + "o_proj.weight");
-        b.load(p + "o_proj.weight", w_o_, dtype_, q_dim_, hidden_, q_dim_);
+        b.load(nq, base, dtype_, hidden_, q_dim_, hidden_);
+        b.load(nk, base + (size_t)q_dim_ * hidden_ * es, dtype_, hidden_, kv_dim_, hidden_);
+        b.load(nv, base + (size_t)(q_dim_ + kv_dim_) * hidden_ * es, dtype_, hidden_, vv_dim_, hidden_);
+        w_o_ = b.allocate((size_t)hidden_ * o_dim_ * es, no);
+        b.load(no, w_o_, dtype_, o_dim_, hidden_, o_dim_);
         if (qk_norm_) {
-            int qd = storage_dtype(b.stored_dtype(p + "q_norm.weight"));
-            int kd = storage_dtype(b.stored_dtype(p + "k_norm.weight"));
+            const std::string qn = p + opt_.names.at("q_norm"), kn = p + opt_.names.at("k_norm");
+            int qd = storage_dtype(b.stored_dtype(qn));
+            int kd = storage_dtype(b.stored_dtype(kn));
             norm_dtype_ = qd == kd ? qd : F32;
-            q_norm_ = b.allocate((size_t)head_dim_ * dtype_size(norm_dtype_), p + "q_norm.weight");
-            k_norm_ = b.allocate((size_t)head_dim_ * dtype_size(norm_dtype_), p + "k_norm.weight");
-            b.load(p + "q_norm.weight", q_norm_, norm_dtype_, head_dim_, 1, head_dim_);
-            b.load(p + "k_norm.weight", k_norm_, norm_dtype_, head_dim_, 1, head_dim_);
+            q_norm_ = b.allocate((size_t)head_dim_ * dtype_size(norm_dtype_), qn);
+            k_norm_ = b.allocate((size_t)head_dim_ * dtype_size(norm_dtype_), kn);
+            b.load(qn, q_norm_, norm_dtype_, head_dim_, 1, head_dim_);
+            b.load(kn, k_norm_, norm_dtype_, head_dim_, 1, head_dim_);
+        }
+        if (opt_.head_mix) {                      // the mix runs in float32
+            const std::string hm = p + opt_.names.at("head_mix");
+            head_mix_ = static_cast<float*>(b.allocate((size_t)heads_ * heads_ * sizeof(float), hm));
+            b.load(hm, head_mix_, F32, heads_, heads_, heads_);
         }
         position_->bind(b, p);
     }
     size_t weight_bytes() const override {
-        size_t n = ((size_t)(q_dim_ + 2 * kv_dim_) * hidden_ + (size_t)hidden_ * q_dim_) * dtype_size(dtype_);
+        size_t n = ((size_t)(q_dim_ + kv_dim_ + vv_dim_) * hidden_ + (size_t)hidden_ * o_dim_) * dtype_size(dtype_);
         if (qk_norm_) n += 2 * (size_t)head_dim_ * dtype_size(norm_dtype_);
+        if (opt_.head_mix) n += (size_t)heads_ * heads_ * sizeof(float);
         return n;
     }
     bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_qkv_, hidden_, w_qkv_, hidden_); }
@@ -406,9 +474,12 @@ private:
     bool qk_norm_;
     float eps_;
     int window_;
+    AttentionOptions opt_;
     float scale_ = 1.f;
-    int q_dim_ = 0, kv_dim_ = 0, dtype_ = BF16, norm_dtype_ = F32;
+    int v_dim_ = 0, q_dim_ = 0, kv_dim_ = 0, vv_dim_ = 0, o_dim_ = 0, dtype_ = BF16, norm_dtype_ = F32;
+    bool mix_path_ = false;
     void *w_qkv_ = nullptr, *w_o_ = nullptr, *q_norm_ = nullptr, *k_norm_ = nullptr;
+    float* head_mix_ = nullptr;
     std::shared_ptr<AttentionPlanner> planner_;
 };
 
@@ -461,34 +532,41 @@ private:
 };
 
 // x += mixer(norm1(x)); x += ffn(norm2(x)): the un-normed x is the residual stream
-// (src/kipp.c:2948, 2994).
+// (src/kipp.c:2948, 2994).  A block without a feed-forward (post_norm and ffn null) has the
+// first sublayer only.
 class PreNormBlock : public Block {
 public:
     PreNormBlock(std::unique_ptr<Norm> n1, std::unique_ptr<Mixer> mixer, std::unique_ptr<Norm> n2,
                  std::unique_ptr<FeedForward> ffn, std::vector<std::string> names)
         : n1_(std::move(n1)), mixer_(std::move(mixer)), n2_(std::move(n2)), ffn_(std::move(ffn)), names_(std::move(names)) {
         if (names_.size() != 4) fail(KIPP_E_CONFIG, "pre_norm_block: four name prefixes are needed");
-        if (n1_->size() != n2_->size()) fail(KIPP_E_CONFIG, "pre_norm_block: the two norms differ in size");
+        if ((n2_ == nullptr) != (ffn_ == nullptr))
+            fail(KIPP_E_CONFIG, "pre_norm_block: post_norm and ffn come together or not at all");
+        if (n2_ && n1_->size() != n2_->size()) fail(KIPP_E_CONFIG, "pre_norm_block: the two norms differ in size");
     }
     void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
         n1_->tensor_specs(p + names_[0], out);
         mixer_->tensor_specs(p + names_[1], out);
-        n2_->tensor_specs(p + names_[2], out);
-        ffn_->tensor_specs(p + names_[3], out);
+        if (ffn_) {
+            n2_->tensor_specs(p + names_[2], out);
+            ffn_->tensor_specs(p + names_[3], out);
+        }
     }
     void bind(Binder& b, const std::string& p) override {
         n1_->bind(b, p + names_[0]);
         mixer_->bind(b, p + names_[1]);
-        n2_->bind(b, p + names_[2]);
-        ffn_->bind(b, p + names_[3]);
+        if (ffn_) {
+            n2_->bind(b, p + names_[2]);
+            ffn_->bind(b, p + names_[3]);
+        }
     }
     size_t weight_bytes() const override {
-        return n1_->weight_bytes() + mixer_->weight_bytes() + n2_->weight_bytes() + ffn_->weight_bytes();
+        return n1_->weight_bytes() + mixer_->weight_bytes() + (ffn_ ? n2_->weight_bytes() + ffn_->weight_bytes() : 0);
     }
     bool graph_safe() const override {
-        return n1_->graph_safe() && mixer_->graph_safe() && n2_->graph_safe() && ffn_->graph_safe();
+        return n1_->graph_safe() && mixer_->graph_safe() && (!ffn_ || (n2_->graph_safe() && ffn_->graph_safe()));
     }
-    std::vector<Mixer*> mixers() override { return {mixer_.get()}; }
+    std::vector<Mixer*> mixers() override { return mixer_->parts(); }
     const Norm* deferred_first_norm() const override {
         return mixer_->folds_rms() && n1_->rms_spec() ? n1_.get() : nullptr;
     }
@@ -500,27 +578,31 @@ public:
     void forward(StepContext& ctx, const LayerRun& run, float* x) override {
         const int T = ctx.tokens();
         void* h = ctx.workspace->buffer("normed", (size_t)T * n1_->size() * ctx.element());
-        const std::optional<RmsNormSpec> spec1 = n1_->rms_spec(), spec2 = n2_->rms_spec();
-        const bool defer1 = spec1 && mixer_->folds_rms(), defer2 = spec2 && ffn_->folds_rms();
+        const std::optional<RmsNormSpec> spec1 = n1_->rms_spec(), spec2 = ffn_ ? n2_->rms_spec() : std::nullopt;
+        const bool defer1 = spec1 && mixer_->folds_rms(), defer2 = ffn_ && spec2 && ffn_->folds_rms();
+        // the norm the next block starts with, if the last residual add of this one may leave its form
+        const Norm* next = ctx.following_norm;
+        const std::optional<RmsNormSpec> spec_next = next ? next->rms_spec() : std::nullopt;
+        const bool next_fits = spec_next && next->size() == n1_->size();
         // -- norm 1 and the mixer
         ctx.input_scale = RowScale{};
         if (defer1 && ctx.pending_norm == n1_.get()) ctx.input_scale = ctx.pending_scale;   // h is made already
         else if (defer1) ctx.input_scale = deferred_norm(ctx, *spec1, x, h);
         else n1_->forward(ctx, x, h, nullptr, T);
         ctx.pending_norm = nullptr;
-        ctx.emit_for = defer2 ? &*spec2 : nullptr;
+        ctx.emit_for = defer2 ? &*spec2 : (!ffn_ && next_fits && mixer_->folds_rms() ? &*spec_next : nullptr);
         ctx.emitted = false;
         mixer_->forward(ctx, run, 0, h, x);
-        // -- norm 2 and the feed-forward
-        ctx.input_scale = RowScale{};
-        if (defer2 && ctx.emitted) ctx.input_scale = ctx.emitted_scale;
-        else if (defer2) ctx.input_scale = deferred_norm(ctx, *spec2, x, h);
-        else n2_->forward(ctx, x, h, nullptr, T);
-        const Norm* next = ctx.following_norm;
-        const std::optional<RmsNormSpec> spec_next = next ? next->rms_spec() : std::nullopt;
-        ctx.emit_for = spec_next && ffn_->folds_rms() && next->size() == n1_->size() ? &*spec_next : nullptr;
-        ctx.emitted = false;
-        ffn_->forward(ctx, h, x);
+        if (ffn_) {
+            // -- norm 2 and the feed-forward
+            ctx.input_scale = RowScale{};
+            if (defer2 && ctx.emitted) ctx.input_scale = ctx.emitted_scale;
+            else if (defer2) ctx.input_scale = deferred_norm(ctx, *spec2, x, h);
+            else n2_->forward(ctx, x, h, nullptr, T);
+            ctx.emit_for = next_fits && ffn_->folds_rms() ? &*spec_next : nullptr;
+            ctx.emitted = false;
+            ffn_->forward(ctx, h, x);
+        }
         if (ctx.emitted) {
             ctx.pending_norm = next;
             ctx.pending_scale = ctx.emitted_scale;
@@ -707,15 +789,17 @@ private:
 inline std::unique_ptr<PositionEncoding> make_position(const Json& j, const BuildContext& ctx) {
     return Registry::get().make_as<PositionEncoding>(j, ctx, "a position encoding");
 }
+void register_recurrent_parts(Registry& r);     // recurrent_parts.hpp
 
 inline void register_builtin_parts() {
     Registry& r = Registry::get();
     r.add_part_kind("token_embedding", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
-        return std::make_unique<TokenEmbedding>((int)j.get("vocab_size").as_int(), (int)j.get("hidden_size").as_int());
+        return std::make_unique<TokenEmbedding>((int)j.get("vocab_size").as_int(), (int)j.get("hidden_size").as_int(),
+                                                j.get_string("weight_name", "weight"));
     });
     r.add_part_kind("output_head", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<OutputHead>((int)j.get("vocab_size").as_int(), (int)j.get("hidden_size").as_int(),
-                                            j.get_string("tied_to", ""));
+                                            j.get_string("tied_to", ""), j.get_string("weight_name", "weight"));
     });
     r.add_part_kind("rmsnorm", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<RMSNorm>((int)j.get("size").as_int(), j.get("eps").as_double(),
@@ -728,8 +812,10 @@ inline void register_builtin_parts() {
         if (rot % 2 || rot < 0 || rot > head_dim)
             fail(KIPP_E_CONFIG, format("rotary_dim %d must be even and at most head_dim %d", rot, head_dim));
         if (!(theta > 0)) fail(KIPP_E_CONFIG, "rotary: theta must be positive");
-        return std::make_unique<FrequencyTable>(rotary_frequencies(rot, theta),
-                                                format("rotary/%.17g/%d", (double)(float)theta, rot));
+        const bool exact = j.get_bool("exact_exponent", false);
+        return std::make_unique<FrequencyTable>(rotary_frequencies(rot, theta, exact),
+                                                format("rotary/%.17g/%d%s", exact ? theta : (double)(float)theta, rot,
+                                                       exact ? "/exact" : ""));
     });
     r.add_part_kind("frequency_table", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         std::vector<float> f;
@@ -743,10 +829,16 @@ inline void register_builtin_parts() {
         std::optional<double> eps, scale;
         if (const Json* e = j.find("qk_norm_eps"); e && !e->is_null()) eps = e->as_double();
         if (const Json* s = j.find("scale"); s && !s->is_null()) scale = s->as_double();
+        AttentionOptions options;
+        options.value_dim = (int)j.get_int("value_dim", 0);
+        options.keep_first = (int)j.get_int("keep_first", 0);
+        options.head_mix = j.get_bool("head_mix", false);
+        options.output_scale = j.get_double("output_scale", 1.0);
+        options.names = tensor_names(j, options.names);
         return std::make_unique<AttentionMixer>(
             (int)j.get("hidden_size").as_int(), (int)j.get("num_heads").as_int(), (int)j.get("num_kv_heads").as_int(),
             (int)j.get("head_dim").as_int(), make_position(j.get("position"), ctx), eps, (int)j.get_int("window", 0),
-            scale);
+            scale, std::move(options));
     });
     r.add_part_kind("swiglu", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<SwiGLUFeedForward>((int)j.get("hidden_size").as_int(),
@@ -756,11 +848,16 @@ inline void register_builtin_parts() {
         const Registry& reg = Registry::get();
         std::vector<std::string> names;
         for (auto& n : j.get("names").items()) names.push_back(n.as_string());
-        return std::make_unique<PreNormBlock>(reg.make_as<Norm>(j.get("input_norm"), ctx, "a norm"),
-                                              reg.make_as<Mixer>(j.get("mixer"), ctx, "a mixer"),
-                                              reg.make_as<Norm>(j.get("post_norm"), ctx, "a norm"),
-                                              reg.make_as<FeedForward>(j.get("ffn"), ctx, "a feed-forward"), names);
+        const Json* n2 = j.find("post_norm");
+        const Json* ff = j.find("ffn");
+        const bool has_ffn = ff != nullptr && !ff->is_null();
+        if (has_ffn && (n2 == nullptr || n2->is_null())) fail(KIPP_E_CONFIG, "pre_norm_block: a feed-forward needs its post_norm");
+        return std::make_unique<PreNormBlock>(
+            reg.make_as<Norm>(j.get("input_norm"), ctx, "a norm"), reg.make_as<Mixer>(j.get("mixer"), ctx, "a mixer"),
+            has_ffn ? reg.make_as<Norm>(*n2, ctx, "a norm") : nullptr,
+            has_ffn ? reg.make_as<FeedForward>(*ff, ctx, "a feed-forward") : nullptr, names);
     });
+    register_recurrent_parts(r);
     r.add_part_kind("external", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
         const std::string role = j.get("role").as_string();
         if (role == "mixer") return std::make_unique<ExternalMixer>(j, ctx);

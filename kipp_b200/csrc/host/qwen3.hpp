@@ -226,8 +226,11 @@ inline Json plan(const Json& c) {
 
 }  // namespace qwen3
 
+void register_venizen();                 // venizen.hpp
+
 inline void register_builtin_architectures() {
     Registry::get().add_architecture("Qwen3ForCausalLM", Architecture{qwen3::normalize, qwen3::plan});
+    register_venizen();
 }
 
 }  // namespace kipp

@@ -1,0 +1,380 @@
+// Mixers that carry a matrix state per request instead of a key/value cache, a mixer made of
+// several mixers side by side, and the feed-forward with a PolyNorm activation.
+//
+//   retention     linear attention with one fixed decay per head, no softmax and no denominator
+//   delta_rule    the generalized delta rule: decay and removal rate per head, key channel and token
+//   parallel      the sum of several mixers that read the same input
+//   polynorm_mlp  W_down act(W_up h), act = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3
+//
+// Every constant (sizes, decays, scales, gates, eps) and every tensor name is a parameter of the
+// plan, so another model can use these parts with other values.  The state is float32
+// [heads, key dim, value dim] per request slot, zeroed by the engine at admission and advanced
+// by exactly the tokens a step brings (kernels in recurrent.cu).
+#pragma once
+#include "parts.hpp"
+
+namespace kipp {
+
+inline float* upload_floats(Binder& b, const std::vector<float>& v, const std::string& what) {
+    float* d = static_cast<float*>(b.allocate(std::max<size_t>(1, v.size()) * sizeof(float), what));
+    if (!v.empty())
+        cuda_check(cudaMemcpy(d, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice), what.c_str());
+    return d;
+}
+inline float* load_f32(Binder& b, const std::string& name, int64_t n) {
+    float* d = static_cast<float*>(b.allocate((size_t)n * sizeof(float), name));
+    b.load(name, d, F32, n, 1, n);
+    return d;
+}
+inline int gate_code(const std::string& g) {
+    if (g == "none") return 0;
+    if (g == "silu") return 1;
+    if (g == "sigmoid") return 2;
+    fail(KIPP_E_CONFIG, "gate must be none, silu or sigmoid, not '" + g + "'");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Retention.  q = W_q h, k = W_k h [heads, dim], v = W_v h [heads, value_dim], no biases; q and k
+// rotated by the position encoding; k scaled by key_scale (default dim^-1/2) after the rotation;
+// per head S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t; each head's o divided by its root
+// mean square (eps inside the root, no weight); heads concatenated, times gate(W_g h), times
+// output_scale, through W_o into the residual stream.
+class RetentionMixer : public Mixer {
+public:
+    RetentionMixer(const Json& j, const BuildContext& ctx) {
+        hidden_ = (int)j.get("hidden_size").as_int();
+        heads_ = (int)j.get("num_heads").as_int();
+        dim_ = (int)j.get("head_dim").as_int();
+        v_dim_ = (int)j.get_int("value_dim", dim_);
+        eps_ = (float)j.get("eps").as_double();
+        out_scale_ = (float)j.get_double("output_scale", 1.0);
+        key_scale_ = (float)j.get_double("key_scale", 1.0 / std::sqrt((double)dim_));
+        gate_ = gate_code(j.get_string("gate", "silu"));
+        for (auto& d : j.get("decay").items()) decay_.push_back((float)d.as_double());
+        position_ = make_position(j.get("position"), ctx);
+        names_ = tensor_names(j, {{"q", "q"}, {"k", "k"}, {"v", "v"}, {"g", "g"}, {"o", "o"}});
+        if (hidden_ <= 0 || heads_ <= 0 || dim_ <= 0 || v_dim_ <= 0) fail(KIPP_E_CONFIG, "retention: sizes must be positive");
+        if ((int)decay_.size() != heads_) fail(KIPP_E_CONFIG, "retention: one decay per head is needed");
+        if (position_->rotary_dim() > dim_ || position_->rotary_dim() % 2)
+            fail(KIPP_E_CONFIG, "retention: rotary_dim must be even and at most head_dim");
+        qk_ = heads_ * dim_;
+        vv_ = heads_ * v_dim_;
+        cols_ = 2 * qk_ + (gate_ ? 2 : 1) * vv_;
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        auto add = [&](const char* role, std::vector<int64_t> shape) {
+            TensorSpec s;
+            s.name = p + names_.at(role);
+            s.shape = std::move(shape);
+            out.push_back(s);
+        };
+        add("q", {qk_, hidden_});
+        add("k", {qk_, hidden_});
+        add("v", {vv_, hidden_});
+        if (gate_) add("g", {vv_, hidden_});
+        add("o", {hidden_, vv_});
+        position_->tensor_specs(p, out);
+    }
+    std::optional<StateSpec> state_spec() const override { return StateSpec{{heads_, dim_, v_dim_}, F32}; }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        // one matrix for q, k, v and the gate so that one product makes them all
+        w_in_ = b.allocate((size_t)cols_ * hidden_ * es, p + "qkvg");
+        char* base = static_cast<char*>(w_in_);
+        b.load(p + names_.at("q"), base, dtype_, hidden_, qk_, hidden_);
+        b.load(p + names_.at("k"), base + (size_t)qk_ * hidden_ * es, dtype_, hidden_, qk_, hidden_);
+        b.load(p + names_.at("v"), base + (size_t)2 * qk_ * hidden_ * es, dtype_, hidden_, vv_, hidden_);
+        if (gate_) b.load(p + names_.at("g"), base + (size_t)(2 * qk_ + vv_) * hidden_ * es, dtype_, hidden_, vv_, hidden_);
+        w_o_ = b.allocate((size_t)hidden_ * vv_ * es, p + names_.at("o"));
+        b.load(p + names_.at("o"), w_o_, dtype_, vv_, hidden_, vv_);
+        decay_dev_ = upload_floats(b, decay_, "retention decays");
+        position_->bind(b, p);
+        if (!Ops::recurrent_scan_ok(dim_, v_dim_, false))
+            fail(KIPP_E_UNSUPPORTED, format("retention: the scan kernel does not take heads of %d x %d", dim_, v_dim_));
+    }
+    size_t weight_bytes() const override { return ((size_t)cols_ + vv_) * hidden_ * dtype_size(dtype_); }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_in_, hidden_, w_in_, hidden_); }
+    void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        const size_t es = ctx.element();
+        Ops& ops = *ctx.ops;
+        const StepMeta& m = *ctx.meta;
+        NormFold fold_in, fold_out;
+        void* proj = ctx.workspace->buffer("retention_proj", (size_t)T * cols_ * es);
+        ops.gemm(proj, ctx.dtype, cols_, h, hidden_, w_in_, hidden_, dtype_, T, cols_, hidden_, EPI_STORE,
+                 fold_input(ctx, fold_in));
+        const float* cos_sin = step_rope_table(ctx, *position_, false);
+        float* state = static_cast<float*>(ctx.state_view(run, mixer_slot, nullptr));
+        void* gated = ctx.workspace->buffer("retention_out", (size_t)T * vv_ * es);
+        ops.retention_scan(gated, vv_, proj, cols_, ctx.dtype, 0, qk_, 2 * qk_, 2 * qk_ + vv_, state, decay_dev_, cos_sin,
+                           position_->rotary_dim(), m.q_start, m.slots, m.shape.entries, heads_, dim_, v_dim_,
+                           key_scale_, eps_, out_scale_, gate_);
+        const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
+        ops.gemm(residual, F32, hidden_, gated, vv_, w_o_, vv_, dtype_, T, hidden_, vv_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
+    }
+
+private:
+    int hidden_ = 0, heads_ = 0, dim_ = 0, v_dim_ = 0, qk_ = 0, vv_ = 0, cols_ = 0, gate_ = 1, dtype_ = BF16;
+    float eps_ = 0.f, out_scale_ = 1.f, key_scale_ = 1.f;
+    std::vector<float> decay_;
+    std::unique_ptr<PositionEncoding> position_;
+    std::map<std::string, std::string> names_;
+    void *w_in_ = nullptr, *w_o_ = nullptr;
+    float* decay_dev_ = nullptr;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Generalized delta rule.  r = W_r h, k = W_k h, v = W_v h, all [heads, dim].  Per head and key
+// channel: decay w = exp(-exp(-1/2) sigmoid(W_w2 tanh(W_w1 h) + w0)), removal rate a =
+// sigmoid(W_a h + a_bias).  With the unit key u = k / sqrt(sum k^2 + 1e-6) of each head:
+// S_t = diag(w) S_{t-1} - (a * u)(u^T S_{t-1}) + k v^T (both terms read the old state), o_t =
+// S_t^T r.  Each head's o divided by its root mean square (eps inside the root), heads
+// concatenated, times the weight `norm`, times gate(W_g h), times output_scale, through W_o.
+class DeltaRuleMixer : public Mixer {
+public:
+    DeltaRuleMixer(const Json& j, const BuildContext&) {
+        hidden_ = (int)j.get("hidden_size").as_int();
+        heads_ = (int)j.get("num_heads").as_int();
+        dim_ = (int)j.get("head_dim").as_int();
+        rank_ = (int)j.get_int("decay_rank", 0);      // 0: the width of the bottleneck is read from its tensor
+        eps_ = (float)j.get("eps").as_double();
+        out_scale_ = (float)j.get_double("output_scale", 1.0);
+        gate_ = gate_code(j.get_string("gate", "sigmoid"));
+        names_ = tensor_names(j, {{"r", "r"}, {"k", "k"}, {"v", "v"}, {"g", "g"}, {"a", "a"}, {"a_bias", "a.b"},
+                                  {"w1", "w1"}, {"w2", "w2"}, {"w_bias", "w0"}, {"norm", "norm"}, {"o", "o"}});
+        if (hidden_ <= 0 || heads_ <= 0 || dim_ <= 0 || rank_ < 0) fail(KIPP_E_CONFIG, "delta_rule: sizes must be positive");
+        hd_ = heads_ * dim_;
+        set_rank(rank_);
+    }
+    // the low-rank bottleneck sits last in the fused projection; rows padded to 16 bytes
+    void set_rank(int rank) {
+        rank_ = rank;
+        cols_ = (gate_ ? 5 : 4) * hd_ + rank_;
+        ld_ = (cols_ + 7) / 8 * 8;
+        rank_ld_ = (rank_ + 7) / 8 * 8;
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
+            TensorSpec s;
+            s.name = p + names_.at(role);
+            s.shape = std::move(shape);
+            s.init = init;
+            out.push_back(s);
+        };
+        add("r", {hd_, hidden_});
+        add("k", {hd_, hidden_});
+        add("v", {hd_, hidden_});
+        if (gate_) add("g", {hd_, hidden_});
+        add("a", {hd_, hidden_});
+        add("a_bias", {hd_});
+        add("w1", {rank_ > 0 ? rank_ : -1, hidden_});
+        add("w2", {hd_, rank_ > 0 ? rank_ : -1});
+        add("w_bias", {hd_});
+        add("norm", {hd_}, "near_one");
+        add("o", {hidden_, hd_});
+    }
+    std::optional<StateSpec> state_spec() const override { return StateSpec{{heads_, dim_, dim_}, F32}; }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        if (rank_ == 0) {
+            const std::vector<int64_t> s1 = b.stored_shape(p + names_.at("w1")), s2 = b.stored_shape(p + names_.at("w2"));
+            if (s1.size() != 2 || s2.size() != 2 || s1[0] <= 0 || s1[0] != s2[1])
+                fail(KIPP_E_WEIGHTS, "delta_rule: " + p + names_.at("w1") + " and " + p + names_.at("w2") +
+                                         " do not agree on the width of the bottleneck");
+            set_rank((int)s1[0]);
+        }
+        // one matrix for r, k, v, the gate, the removal rate and the decay's bottleneck
+        w_in_ = b.allocate((size_t)cols_ * hidden_ * es, p + "rkvgaw");
+        char* base = static_cast<char*>(w_in_);
+        int row = 0;
+        auto put = [&](const char* role, int rows) {
+            b.load(p + names_.at(role), base + (size_t)row * hidden_ * es, dtype_, hidden_, rows, hidden_);
+            row += rows;
+        };
+        put("r", hd_);
+        put("k", hd_);
+        put("v", hd_);
+        if (gate_) put("g", hd_);
+        put("a", hd_);
+        put("w1", rank_);
+        // the bottleneck's rows of W_w2 are padded to a multiple of 8 elements (zeros beyond the rank)
+        w2_ = b.allocate((size_t)hd_ * rank_ld_ * es, p + names_.at("w2"));
+        cuda_check(cudaMemset(w2_, 0, (size_t)hd_ * rank_ld_ * es), "clearing a padded weight");
+        b.load(p + names_.at("w2"), w2_, dtype_, rank_ld_, hd_, rank_);
+        w_o_ = b.allocate((size_t)hidden_ * hd_ * es, p + names_.at("o"));
+        b.load(p + names_.at("o"), w_o_, dtype_, hd_, hidden_, hd_);
+        a_bias_ = load_f32(b, p + names_.at("a_bias"), hd_);
+        w_bias_ = load_f32(b, p + names_.at("w_bias"), hd_);
+        norm_ = load_f32(b, p + names_.at("norm"), hd_);
+        if (!Ops::recurrent_scan_ok(dim_, dim_, true))
+            fail(KIPP_E_UNSUPPORTED, format("delta_rule: the scan kernel does not take heads of %d x %d", dim_, dim_));
+    }
+    size_t weight_bytes() const override {
+        return ((size_t)cols_ * hidden_ + (size_t)hd_ * rank_ + (size_t)hidden_ * hd_) * dtype_size(dtype_) + (size_t)3 * hd_ * 4;
+    }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_in_, hidden_, w_in_, hidden_); }
+    void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        const size_t es = ctx.element();
+        Ops& ops = *ctx.ops;
+        const StepMeta& m = *ctx.meta;
+        NormFold fold_in, fold_out;
+        void* proj = ctx.workspace->buffer("delta_proj", (size_t)T * ld_ * es);
+        ops.gemm(proj, ctx.dtype, ld_, h, hidden_, w_in_, hidden_, dtype_, T, cols_, hidden_, EPI_STORE,
+                 fold_input(ctx, fold_in));
+        const int g_off = 3 * hd_, a_off = (gate_ ? 4 : 3) * hd_, w1_off = a_off + hd_;
+        // the decay: tanh of the bottleneck, then its second product; the bias and the squashing
+        // are the scan kernel's, in float32
+        void* low = ctx.workspace->buffer("delta_low_rank", (size_t)T * rank_ld_ * es);
+        if (rank_ld_ != rank_) cuda_check(cudaMemsetAsync(low, 0, (size_t)T * rank_ld_ * es, ctx.stream), "clearing the bottleneck");
+        ops.tanh_rows(low, rank_ld_, static_cast<const char*>(proj) + (size_t)w1_off * es, ld_, ctx.dtype, T, rank_);
+        void* w_raw = ctx.workspace->buffer("delta_decay", (size_t)T * hd_ * es);
+        ops.gemm(w_raw, ctx.dtype, hd_, low, rank_ld_, w2_, rank_ld_, dtype_, T, hd_, rank_ld_, EPI_STORE);
+        float* state = static_cast<float*>(ctx.state_view(run, mixer_slot, nullptr));
+        void* gated = ctx.workspace->buffer("delta_out", (size_t)T * hd_ * es);
+        ops.delta_rule_scan(gated, hd_, proj, ld_, ctx.dtype, 0, hd_, 2 * hd_, g_off, a_off, w_raw, hd_, a_bias_, w_bias_,
+                            norm_, state, m.q_start, m.slots, m.shape.entries, heads_, dim_, eps_, out_scale_, gate_);
+        const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
+        ops.gemm(residual, F32, hidden_, gated, hd_, w_o_, hd_, dtype_, T, hidden_, hd_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
+    }
+
+private:
+    int hidden_ = 0, heads_ = 0, dim_ = 0, rank_ = 0, rank_ld_ = 0, hd_ = 0, cols_ = 0, ld_ = 0, gate_ = 2, dtype_ = BF16;
+    float eps_ = 0.f, out_scale_ = 1.f;
+    std::map<std::string, std::string> names_;
+    void *w_in_ = nullptr, *w2_ = nullptr, *w_o_ = nullptr;
+    float *a_bias_ = nullptr, *w_bias_ = nullptr, *norm_ = nullptr;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Several mixers side by side: each reads the same input and adds its (scaled) output to the
+// residual stream; each has its own cache or state (mixer slot = its index).  The scale of a
+// branch is that mixer's own output_scale.
+class ParallelMixer : public Mixer {
+public:
+    ParallelMixer(const Json& j, const BuildContext& ctx) {
+        for (auto& b : j.get("branches").items()) {
+            prefixes_.push_back(b.get_string("prefix", ""));
+            branches_.push_back(Registry::get().make_as<Mixer>(b.get("part"), ctx, "a mixer"));
+        }
+        if (branches_.empty()) fail(KIPP_E_CONFIG, "parallel: at least one branch is needed");
+        if (branches_.size() > 16) fail(KIPP_E_CONFIG, "parallel: at most 16 branches");
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        for (size_t i = 0; i < branches_.size(); ++i) branches_[i]->tensor_specs(p + prefixes_[i], out);
+    }
+    void bind(Binder& b, const std::string& p) override {
+        for (size_t i = 0; i < branches_.size(); ++i) branches_[i]->bind(b, p + prefixes_[i]);
+    }
+    size_t weight_bytes() const override {
+        size_t n = 0;
+        for (auto& m : branches_) n += m->weight_bytes();
+        return n;
+    }
+    bool graph_safe() const override {
+        for (auto& m : branches_)
+            if (!m->graph_safe()) return false;
+        return true;
+    }
+    bool folds_rms() const override {
+        for (auto& m : branches_)
+            if (!m->folds_rms()) return false;
+        return true;
+    }
+    std::vector<Mixer*> parts() override {
+        std::vector<Mixer*> v;
+        for (auto& m : branches_) v.push_back(m.get());
+        return v;
+    }
+    void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) override {
+        // only the last residual add may leave the next norm's deferred form: the stream is
+        // complete only then
+        const RmsNormSpec* emit_for = ctx.emit_for;
+        for (size_t i = 0; i < branches_.size(); ++i) {
+            ctx.emit_for = i + 1 == branches_.size() ? emit_for : nullptr;
+            branches_[i]->forward(ctx, run, mixer_slot + (int)i, h, residual);
+        }
+    }
+
+private:
+    std::vector<std::string> prefixes_;
+    std::vector<std::unique_ptr<Mixer>> branches_;
+};
+
+// ---------------------------------------------------------------------------------------------
+// x += W_down act(W_up n), act = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 with powers taken element
+// by element and N the division of a token's vector by its root mean square (eps inside the
+// root).  The four numbers are the tensor `act`.
+class PolyNormFeedForward : public FeedForward {
+public:
+    explicit PolyNormFeedForward(const Json& j) {
+        hidden_ = (int)j.get("hidden_size").as_int();
+        inter_ = (int)j.get("intermediate_size").as_int();
+        eps_ = (float)j.get("eps").as_double();
+        names_ = tensor_names(j, {{"up", "up"}, {"down", "down"}, {"act", "act"}});
+        if (hidden_ <= 0 || inter_ <= 0) fail(KIPP_E_CONFIG, "polynorm_mlp: sizes must be positive");
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
+            TensorSpec s;
+            s.name = p + names_.at(role);
+            s.shape = std::move(shape);
+            s.init = init;
+            out.push_back(s);
+        };
+        add("up", {inter_, hidden_});
+        add("down", {hidden_, inter_});
+        add("act", {4}, "near_one");
+    }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        w_up_ = b.allocate((size_t)inter_ * hidden_ * es, p + names_.at("up"));
+        b.load(p + names_.at("up"), w_up_, dtype_, hidden_, inter_, hidden_);
+        w_down_ = b.allocate((size_t)hidden_ * inter_ * es, p + names_.at("down"));
+        b.load(p + names_.at("down"), w_down_, dtype_, inter_, hidden_, inter_);
+        coef_ = load_f32(b, p + names_.at("act"), 4);
+    }
+    size_t weight_bytes() const override { return (size_t)2 * inter_ * hidden_ * dtype_size(dtype_) + 16; }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_up_, hidden_, w_up_, hidden_); }
+    void forward(StepContext& ctx, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        NormFold in, out;
+        void* z = ctx.workspace->buffer("ffn_up", (size_t)T * inter_ * ctx.element());
+        ctx.ops->gemm(z, ctx.dtype, inter_, h, hidden_, w_up_, hidden_, dtype_, T, inter_, hidden_, EPI_STORE,
+                      fold_input(ctx, in));
+        void* act = ctx.workspace->buffer("ffn_act", (size_t)T * inter_ * ctx.element());
+        ctx.ops->polynorm(act, inter_, z, inter_, ctx.dtype, coef_, T, inter_, eps_);
+        const NormFold* emit = fold_emit(ctx, out, hidden_);
+        ctx.ops->gemm(residual, F32, hidden_, act, inter_, w_down_, inter_, dtype_, T, hidden_, inter_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
+    }
+
+private:
+    int hidden_ = 0, inter_ = 0, dtype_ = BF16;
+    float eps_ = 0.f;
+    std::map<std::string, std::string> names_;
+    void *w_up_ = nullptr, *w_down_ = nullptr;
+    float* coef_ = nullptr;
+};
+
+inline void register_recurrent_parts(Registry& r) {
+    r.add_part_kind("retention", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        return std::make_unique<RetentionMixer>(j, ctx);
+    });
+    r.add_part_kind("delta_rule", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        return std::make_unique<DeltaRuleMixer>(j, ctx);
+    });
+    r.add_part_kind("parallel", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        return std::make_unique<ParallelMixer>(j, ctx);
+    });
+    r.add_part_kind("polynorm_mlp", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
+        return std::make_unique<PolyNormFeedForward>(j);
+    });
+}
+
+}  // namespace kipp

@@ -34,6 +34,7 @@ struct SchedulerHost {
     int page_size = 16;
     std::vector<int> group_pages;
     std::vector<int> group_windows;          // 0: every key is kept
+    std::vector<int> group_keep_first;       // positions a window group never gives back (may be shorter: 0)
     int max_requests = 1;
     int max_batch_tokens = 1;
     long long max_positions = 0;             // 0: no limit
@@ -250,7 +251,8 @@ public:
         const int window = host_.group_windows[(size_t)group];
         if (window <= 0) return full;
         const int span = window - 1 + step_cap();
-        return std::min(full, (span + page - 1) / page + 1);
+        const int kept = (size_t)group < host_.group_keep_first.size() ? host_.group_keep_first[(size_t)group] : 0;
+        return std::min(full, (span + page - 1) / page + 1 + (kept + page - 1) / page);
     }
 
 private:
@@ -360,6 +362,7 @@ inline SchedulerHost engine_scheduler_host(Engine& e) {
     for (int g = 0; g < e.groups(); ++g) {
         h.group_pages.push_back(e.group_pages(g));
         h.group_windows.push_back(e.group_window(g));
+        h.group_keep_first.push_back(e.group_keep_first(g));
     }
     h.max_requests = e.options().max_requests;
     h.max_batch_tokens = e.options().max_batch_tokens;

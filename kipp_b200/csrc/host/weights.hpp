@@ -74,6 +74,15 @@ struct StoredTensor {
     }
 };
 
+// Whether a stored shape is what a spec asks for; a spec's -1 leaves that size open (the part
+// reads it from the tensor when it binds).
+inline bool shape_fits(const std::vector<int64_t>& stored, const std::vector<int64_t>& wanted) {
+    if (stored.size() != wanted.size()) return false;
+    for (size_t i = 0; i < stored.size(); ++i)
+        if (wanted[i] >= 0 ? stored[i] != wanted[i] : stored[i] <= 0) return false;
+    return true;
+}
+
 inline std::string shape_text(const std::vector<int64_t>& shape) {
     std::string s = "[";
     for (size_t i = 0; i < shape.size(); ++i) s += (i ? ", " : "") + std::to_string(shape[i]);
@@ -213,7 +222,7 @@ public:
                 r.missing.push_back(s.name);
                 continue;
             }
-            if (t->shape != s.shape) r.wrong_shape.emplace_back(s.name, t->shape, s.shape);
+            if (!shape_fits(t->shape, s.shape)) r.wrong_shape.emplace_back(s.name, t->shape, s.shape);
             if (t->dtype < 0) r.wrong_dtype.emplace_back(s.name, t->dtype_text);
         }
         for (auto& t : tensors_)

@@ -62,7 +62,7 @@ __global__ void qk_norm_rope_write_kernel(
     const float2* __restrict__ cos_sin, int rotary_dim,
     const int* __restrict__ positions, const int* __restrict__ entry_of_token,
     const int* __restrict__ block_table, int table_width, int page_size,
-    int tokens, int n_q, int n_kv, int head_dim, int write_cache, int* __restrict__ status) {
+    int tokens, int n_q, int n_kv, int head_dim, int v_dim, int write_cache, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -74,7 +74,10 @@ __global__ void qk_norm_rope_write_kernel(
     const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
     if (!is_q && !(write_cache & 1)) return;
     const bool rnd = !is_q && (write_cache & 2), kv = !is_q;
-    const T* src = qkv + (size_t)t * ld_qkv + (size_t)h * head_dim;
+    // value heads have v_dim elements (in the projection and in the pages), the others head_dim
+    const bool is_v = !is_q && !is_k;
+    const T* src = qkv + (size_t)t * ld_qkv +
+                   (is_v ? (size_t)(n_q + n_kv) * head_dim + (size_t)(h - n_q - n_kv) * v_dim : (size_t)h * head_dim);
     const int pos = positions[t];
 
     T* dst;
@@ -90,18 +93,18 @@ __global__ void qk_norm_rope_write_kernel(
         }
         const int g = is_k ? h - n_q : h - n_q - n_kv;
         T* base = is_k ? k_pages : v_pages;
-        dst = base + (((size_t)page * n_kv + g) * page_size + (pos % page_size)) * head_dim;
+        dst = base + (((size_t)page * n_kv + g) * page_size + (pos % page_size)) * (is_k ? head_dim : v_dim);
     }
 
-    if (!is_q && !is_k) {                     // values: copy
+    if (is_v) {                               // values: copy
         if constexpr (V == 2) {
-            for (int i = 2 * lane; i < head_dim; i += 64) {
+            for (int i = 2 * lane; i < v_dim; i += 64) {
                 float a, b;
                 load2(src + i, a, b);
                 store2(dst + i, stored(a, rnd, true), stored(b, rnd, true));
             }
         } else {
-            for (int i = lane; i < head_dim; i += 32) dst[i] = from_f32<T>(stored(to_f32(src[i]), rnd, true));
+            for (int i = lane; i < v_dim; i += 32) dst[i] = from_f32<T>(stored(to_f32(src[i]), rnd, true));
         }
         return;
     }
@@ -210,15 +213,15 @@ template <typename T>
 int launch_rope(const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v_pages, const void* q_norm_w,
                 const void* k_norm_w, int norm_dtype, float eps, const float2* cos_sin, int rotary_dim,
                 const int* positions, const int* entry_of_token, const int* block_table, int table_width,
-                int page_size, int tokens, int n_q, int n_kv, int head_dim, int write_cache, int* status,
+                int page_size, int tokens, int n_q, int n_kv, int head_dim, int v_dim, int write_cache, int* status,
                 unsigned blocks, int threads, cudaStream_t s) {
     // adjacent elements side by side only when pairs of them stay inside one half
-    const bool two = head_dim % 4 == 0 && ld_qkv % 2 == 0 && ((uintptr_t)qkv & 7) == 0 &&
+    const bool two = head_dim % 4 == 0 && v_dim % 2 == 0 && ld_qkv % 2 == 0 && ((uintptr_t)qkv & 7) == 0 &&
                      ((uintptr_t)q_out & 7) == 0 && ((uintptr_t)k_pages & 7) == 0 && ((uintptr_t)v_pages & 7) == 0;
     auto kernel = two ? qk_norm_rope_write_kernel<T, 2> : qk_norm_rope_write_kernel<T, 1>;
     return kipp_launch(kernel, dim3(blocks), dim3(threads), 0, s, 1, (const T*)qkv, ld_qkv, (T*)q_out, (T*)k_pages,
                        (T*)v_pages, q_norm_w, k_norm_w, norm_dtype, eps, cos_sin, rotary_dim, positions,
-                       entry_of_token, block_table, table_width, page_size, tokens, n_q, n_kv, head_dim,
+                       entry_of_token, block_table, table_width, page_size, tokens, n_q, n_kv, head_dim, v_dim,
                        write_cache, status);
 }
 // Fast path for bfloat16 with head_dim 64, 128 or 256 and a rotation over the
@@ -359,13 +362,15 @@ extern "C" int kipp_rope_table_by_pair(void* out, const int* positions, const fl
                        (float2*)out, positions, inv_freq, tokens, half, 1);
 }
 
-extern "C" int kipp_qk_norm_rope_write(
+// The same with value heads of v_dim elements (in the projection, after the keys, and in the value pages).
+extern "C" int kipp_qk_norm_rope_write_v(
     const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v_pages, int dtype,
     const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
     const void* cos_sin, int rotary_dim, const int* positions, const int* entry_of_token,
     const int* block_table, int table_width, int page_size, int tokens, int n_q, int n_kv,
-    int head_dim, int write_cache, int* status, void* stream) {
+    int head_dim, int v_dim, int write_cache, int* status, void* stream) {
     if (tokens <= 0) return 0;
+    if (v_dim <= 0) return KIPP_ERR_ARG;
     if (head_dim <= 0 || (head_dim & 1) || head_dim > 64 * MAX_PER_LANE) return KIPP_ERR_ARG;
     if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return KIPP_ERR_ARG;
     if (page_size <= 0 || n_q <= 0 || n_kv <= 0) return KIPP_ERR_ARG;
@@ -379,7 +384,7 @@ extern "C" int kipp_qk_norm_rope_write(
                            (uintptr_t)q_norm_w | (uintptr_t)k_norm_w | (uintptr_t)cos_sin) & 15) == 0;
     if (dtype == KIPP_DT_BF16 && aligned && ld_qkv % 8 == 0 && tokens <= 65535 &&
         (cos_sin == nullptr || rotary_dim == head_dim) && (q_norm_w == nullptr) == (k_norm_w == nullptr) &&
-        (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+        (head_dim == 64 || head_dim == 128 || head_dim == 256) && v_dim == head_dim) {
         const float2* cs = rotary_dim == 0 ? nullptr : (const float2*)cos_sin;
         if (head_dim == 64)
             return launch_rope_bf16<64>(qkv, ld_qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, norm_dtype, eps, cs,
@@ -396,12 +401,23 @@ extern "C" int kipp_qk_norm_rope_write(
     if (dtype == KIPP_DT_F32)
         return launch_rope<float>(qkv, ld_qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, norm_dtype, eps,
                                   (const float2*)cos_sin, rotary_dim, positions, entry_of_token, block_table, table_width,
-                                  page_size, tokens, n_q, n_kv, head_dim, write_cache, status, (unsigned)blocks,
+                                  page_size, tokens, n_q, n_kv, head_dim, v_dim, write_cache, status, (unsigned)blocks,
                                   threads, s);
     if (dtype == KIPP_DT_BF16)
         return launch_rope<bf16>(qkv, ld_qkv, q_out, k_pages, v_pages, q_norm_w, k_norm_w, norm_dtype, eps,
                                  (const float2*)cos_sin, rotary_dim, positions, entry_of_token, block_table, table_width,
-                                 page_size, tokens, n_q, n_kv, head_dim, write_cache, status, (unsigned)blocks,
+                                 page_size, tokens, n_q, n_kv, head_dim, v_dim, write_cache, status, (unsigned)blocks,
                                  threads, s);
     return KIPP_ERR_DTYPE;
+}
+
+extern "C" int kipp_qk_norm_rope_write(
+    const void* qkv, int ld_qkv, void* q_out, void* k_pages, void* v_pages, int dtype,
+    const void* q_norm_w, const void* k_norm_w, int norm_dtype, float eps,
+    const void* cos_sin, int rotary_dim, const int* positions, const int* entry_of_token,
+    const int* block_table, int table_width, int page_size, int tokens, int n_q, int n_kv,
+    int head_dim, int write_cache, int* status, void* stream) {
+    return kipp_qk_norm_rope_write_v(qkv, ld_qkv, q_out, k_pages, v_pages, dtype, q_norm_w, k_norm_w, norm_dtype, eps,
+                                     cos_sin, rotary_dim, positions, entry_of_token, block_table, table_width,
+                                     page_size, tokens, n_q, n_kv, head_dim, head_dim, write_cache, status, stream);
 }

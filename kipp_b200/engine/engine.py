@@ -23,7 +23,7 @@ import torch
 from .. import native as N
 from ..cache import CacheManager
 from ..cache import _native as cache_native
-from ..config.base import ConfigError, ModelConfig, read_config_json
+from ..config.base import ConfigError, ModelConfig, architecture_name, read_config_json
 from ..config.registry import get_architecture, is_registered
 from ..models.spec import LayerRun, ModelSpec
 from ..parts.base import PagedKVSpec
@@ -244,10 +244,7 @@ class Engine:
         chosen by ``architectures[0]``: an architecture registered from Python if
         there is one of that name, else the library's own registry."""
         data = read_config_json(folder)
-        archs = data.get("architectures") if isinstance(data, dict) else None
-        if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-            raise ConfigError("config.json lacks 'architectures': [name]")
-        arch = get_architecture(archs[0])         # raises ConfigError for a name nobody knows
+        arch = get_architecture(architecture_name(data))   # raises ConfigError for a name nobody knows
         config = arch.config_class.from_dict(data)
         spec = arch.build(config)
         return cls(spec, None, folder=folder, **options)

@@ -15,7 +15,7 @@ import torch
 
 from ..config.base import ModelConfig
 from .safetensors_io import write_safetensors
-from .spec import INIT_INT, INIT_NEAR_ONE, INIT_NORMAL, TensorSpec
+from .spec import INIT_INT, INIT_NEAR_IDENTITY, INIT_NEAR_ONE, INIT_NORMAL, TensorSpec
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -33,6 +33,8 @@ def random_tensors(specs: Iterable[TensorSpec], seed: int, *, sigma: float = 0.0
     for s in specs:
         if skip_aliased and s.optional and s.alias_of is not None:
             continue
+        if any(d < 0 for d in s.shape):
+            raise ValueError(f"{s.name}: a size the configuration leaves open cannot be made from a seed")
         gen = torch.Generator(device=device)
         gen.manual_seed(_tensor_seed(seed, s.name))
         if s.init == INIT_NORMAL:
@@ -40,6 +42,9 @@ def random_tensors(specs: Iterable[TensorSpec], seed: int, *, sigma: float = 0.0
         elif s.init == INIT_NEAR_ONE:
             t = torch.empty(s.shape, dtype=torch.float32, device=device).uniform_(-norm_jitter, norm_jitter, generator=gen)
             t += 1.0
+        elif s.init == INIT_NEAR_IDENTITY:
+            t = torch.empty(s.shape, dtype=torch.float32, device=device).normal_(0.0, norm_jitter, generator=gen)
+            t += torch.eye(s.shape[0], s.shape[1], dtype=torch.float32, device=device)
         elif s.init == INIT_INT:
             yield s.name, torch.zeros(s.shape, dtype=torch.int32, device=device)
             continue

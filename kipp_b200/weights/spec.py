@@ -7,6 +7,7 @@ import dataclasses
 INIT_NORMAL = "normal"            # N(0, sigma)
 INIT_NEAR_ONE = "near_one"        # 1 + U(-a, a): norm scales
 INIT_INT = "int"                  # integer table
+INIT_NEAR_IDENTITY = "near_identity"   # I + N(0, sigma): a square matrix that mixes heads
 
 
 @dataclasses.dataclass(frozen=True)
