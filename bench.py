@@ -126,6 +126,105 @@ def reference_arm(args) -> int:
     return ref.main(args, dict(config), WEIGHT_SEED, POINT_PROMPT, PREFILL_TOKENS)
 
 
+# ---- the Venizen design beside the Qwen3 design at equal layer sizes (--designs) ------------------
+# (width, heads, kv heads, head size, feed-forward width, layers): layers of real models' sizes
+DESIGN_SIZES = {"1b": (2048, 16, 4, 128, 6144, 4), "4b": (2560, 32, 8, 128, 9728, 4), "8b": (4096, 32, 8, 128, 12288, 2)}
+DESIGN_WINDOW, DESIGN_KEEP = 1024, 4
+
+
+def venizen_of(size: str, vocab: int = 32000) -> dict:
+    """Half of the layers attention beside retention with a PolyNorm feed-forward, half the
+    generalized delta rule without one (the design's two kinds), no loop."""
+    width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                              "mask": {"size": DESIGN_WINDOW, "keep_first": DESIGN_KEEP},
+                              "rot": {"base": 1e6, "dims": dim}, "scale": dim ** -0.5},
+                     "right": {"heads": heads // 2, "dim": 64, "vdim": dim, "decay": [1 - 2.0 ** -(5 + i % 4) for i in range(heads // 2)],
+                               "rot": {"base": 1e4, "dims": 64}},
+                     "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "dense", "ff": ff}}
+    delta = {"type": "general_delta", "mixer": {"heads": heads, "dim": dim // 2, "decay_rank": 64}, "mlp": None}
+    return {"architecture": "Venizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [par if i % 2 == 0 else delta for i in range(layers)], "loop": None}
+
+
+def qwen3_of(size: str, vocab: int = 32000) -> dict:
+    width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
+    return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=vocab, hidden_size=width,
+                intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv,
+                head_dim=dim, max_position_embeddings=32768, rope_theta=1e6, rms_norm_eps=1e-6,
+                tie_word_embeddings=False, hidden_act="silu", attention_bias=False, initializer_range=0.02,
+                torch_dtype="bfloat16", sliding_window=DESIGN_WINDOW, layer_types=["sliding_attention"] * layers)
+
+
+def compare_designs(args) -> int:
+    """Prefill and decode throughput of Venizen beside Qwen3 at equal layer sizes (random
+    weights), with the time of every kernel of a prompt step and of a decode step (an event
+    after every launch).  Prints ONE JSON line; the default workload's record is not touched."""
+    import torch
+    from kipp_b200.config import config_from_dict
+    from kipp_b200.engine import Engine, StepEntry
+    pk, pk_src = peaks()
+    T, B, ctx = args.designs_prompt, args.batch, args.designs_prompt
+    out = {"metric": "prefill and decode tokens/s, Venizen beside Qwen3 at equal layer sizes", "dtype": "bf16",
+           "data": "synthetic: random weights, seeded random token ids", "prompt_tokens": T, "decode_batch": B,
+           "decode_context": ctx, "window": DESIGN_WINDOW, "peaks": pk, "peak_source": pk_src, "sizes": {}}
+    g = torch.Generator().manual_seed(99)
+    for size in args.designs.split(","):
+        row = {}
+        for design, cfg in (("venizen", venizen_of(size)), ("qwen3", qwen3_of(size))):
+            config = config_from_dict(cfg)
+            eng = Engine.from_config(config, 7, dtype="bfloat16", page_size=PAGE, cache_tokens=(B + 1) * (ctx + 512),
+                                     max_requests=B + 1, max_batch_tokens=max(T, B))
+            stream, dev = eng.stream, eng.runtime.device
+            toks = torch.randint(0, config.vocab_size, (T,), generator=g).tolist()
+
+            def timed(fn, runs):
+                ms = []
+                for i in range(runs):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize(dev)
+                    a.record(stream)
+                    fn(i)
+                    b.record(stream)
+                    torch.cuda.synchronize(dev)
+                    ms.append(a.elapsed_time(b))
+                return statistics.median(ms)
+
+            def one_prefill(i):
+                eng.step([StepEntry(("p", i), toks, [T - 1])])
+                eng.finish(("p", i))
+            timed(one_prefill, 3)
+            prefill_ms = timed(lambda i: one_prefill(100 + i), 5)
+            eng.profile_start()
+            one_prefill(1000)
+            prefill_kernels = eng.profile_stop()
+            rids = [("d", i) for i in range(B)]
+            for r in rids:
+                eng.step([StepEntry(r, toks[:ctx], [])])
+            cur = toks[:B]
+            eng.decode_burst(rids, cur, 8)
+            decode_ms = timed(lambda i: eng.decode_burst(rids, cur, args.steps), 3) / args.steps
+            eng.profile_start()
+            eng.decode_burst(rids, cur, 2)
+            decode_kernels = {k: v / 2 for k, v in eng.profile_stop().items()}
+            row[design] = {"prefill_tokens_per_s": round(T / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                           "decode_tokens_per_s": round(B / (decode_ms / 1e3), 1), "decode_ms_per_step": round(decode_ms, 4),
+                           "weight_gb": round(eng.weight_bytes() / 1e9, 3),
+                           "decode_hbm_frac": round(eng.weight_bytes() / (decode_ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                           "prefill_kernels_ms": {k: round(v, 4) for k, v in sorted(prefill_kernels.items(), key=lambda kv: -kv[1])},
+                           "decode_kernels_ms": {k: round(v, 4) for k, v in sorted(decode_kernels.items(), key=lambda kv: -kv[1])}}
+            for r in rids:
+                eng.finish(r)
+            eng.runtime.check_status()
+            del eng
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+    print(json.dumps(out))
+    return 0
+
+
 def median_mad(values: list) -> tuple[float, float]:
     """Median and median absolute deviation (the reference's policy for its own
     benchmark figures, tools/bench.py:260-268)."""
@@ -148,9 +247,15 @@ def main() -> int:
     ap.add_argument("--preset", default="qwen3-4b", help="another preset's sizes (the record names them)")
     ap.add_argument("--own-length-splits", action="store_true",
                     help="decode attention splits from each token's own context only")
+    ap.add_argument("--designs", default=None, metavar="SIZES",
+                    help="instead of the default workload: the Venizen design beside Qwen3 at equal layer sizes, "
+                         f"a list of {','.join(DESIGN_SIZES)} (prefill and decode tokens/s, time per kernel)")
+    ap.add_argument("--designs-prompt", type=int, default=2048, help="prompt and decode context of --designs")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.designs:
+        return compare_designs(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

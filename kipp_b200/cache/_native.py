@@ -26,6 +26,7 @@ _SIGNATURES = {
     "kipp_slots_alloc": (_i, [_vp, _ll]), "kipp_slots_free": (_i, [_vp, _i, _ll]),
     "kipp_slots_free_count": (_i, [_vp]), "kipp_slots_check": (_i, [_vp]),
     "kipp_cm_create": (_vp, [_i, _ip, _ip, _i, _i]), "kipp_cm_destroy": (None, [_vp]),
+    "kipp_cm_set_keep_first": (_i, [_vp, _i, _i]),
     "kipp_cm_pool": (_vp, [_vp, _i]), "kipp_cm_slots": (_vp, [_vp]),
     "kipp_cm_admit": (_i, [_vp, _ll]), "kipp_cm_release": (_i, [_vp, _ll]),
     "kipp_cm_slot": (_i, [_vp, _ll]), "kipp_cm_length": (_i, [_vp, _ll]),

@@ -71,11 +71,13 @@ class CacheGroup:
         if self.window is None:
             return full
         span = self.window - 1 + max_step_tokens
-        return min(full, -(-span // self.page_size) + 1)
+        kept = -(-int(getattr(self.spec, "keep_first", 0) or 0) // self.page_size)    # pages the window never gives back
+        return min(full, -(-span // self.page_size) + 1 + kept)
 
     def bytes_per_page(self, element_size: int) -> int:
-        return (2 * len(self.cache_ids) * self.spec.kv_heads * self.page_size
-                * self.spec.head_dim * element_size)
+        value_dim = getattr(self.spec, "value_dim", None) or self.spec.head_dim
+        return (len(self.cache_ids) * self.spec.kv_heads * self.page_size
+                * (self.spec.head_dim + value_dim) * element_size)
 
 
 class CacheManager:
@@ -107,6 +109,10 @@ class CacheManager:
         self._h = self._lib.kipp_cm_create(ng, pages, windows, page_size, max_requests)
         if not self._h:
             raise ValueError("the cache manager could not be created")
+        for gi, g in enumerate(self.groups):
+            keep = int(getattr(g.spec, "keep_first", 0) or 0)
+            if g.window is not None and keep > 0:
+                self._lib.kipp_cm_set_keep_first(self._h, gi, keep)
         self._owners = N.OwnerIds()
         for gi, g in enumerate(self.groups):
             g.pool = PagePool(g.n_pages, _handle=self._lib.kipp_cm_pool(self._h, gi), _owners=self._owners,

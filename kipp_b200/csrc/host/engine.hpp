@@ -1095,8 +1095,12 @@ inline void Engine::debug_part(const StepEntryView* entries, int n, int run_inde
         need_pre()->input_norm()->forward(ctx, residual, output, nullptr, T);
     } else if (which == "post_norm") {
         need_pre()->post_norm()->forward(ctx, residual, output, nullptr, T);
-    } else if (which == "mixer") {
-        block->mixers().at(0)->forward(ctx, run, 0, input, residual);
+    } else if (which == "mixer" || which.rfind("mixer/", 0) == 0) {
+        // "mixer/<k>": the k-th of the mixers a block holds side by side, with its own cache or state
+        const int k = which == "mixer" ? 0 : atoi(which.c_str() + 6);
+        auto mixers = block->mixers();
+        if (k < 0 || k >= (int)mixers.size()) fail(KIPP_E_ARGUMENT, "the block has no mixer " + std::to_string(k));
+        mixers[(size_t)k]->forward(ctx, run, k, input, residual);
     } else if (which == "feed_forward") {
         need_pre()->feed_forward()->forward(ctx, input, residual);
     } else if (which == "block") {

@@ -224,7 +224,8 @@ class Engine:
         self.runtime = _Runtime(self)
         info = self.info()
         self.vocab_size = info["vocab_size"]
-        groups = [(PagedKVSpec(g["kv_heads"], g["head_dim"], g["window"]), g["caches"], g["pages"])
+        groups = [(PagedKVSpec(g["kv_heads"], g["head_dim"], g["window"], g.get("value_dim"), g.get("keep_first", 0)),
+                   g["caches"], g["pages"])
                   for g in info["cache_groups"]]
         self.cache = CacheManager.view_of(self._lib.kipp_engine_cache_manager(self._h), groups, page_size,
                                           max_requests, self._owners, keep=self)

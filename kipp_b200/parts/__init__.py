@@ -5,8 +5,10 @@ from .block import PreNormBlock
 from .embedding import OutputHead, TokenEmbedding
 from .mlp import SwiGLUFeedForward
 from .norm import RMSNorm
+from .recurrent import DeltaRuleMixer, ParallelMixer, PolyNormFeedForward, RetentionMixer
 from .rope import NoPositionEncoding, RotaryEncoding
 
 __all__ = ["AttentionMixer", "Block", "EmbeddingStage", "FeedForward", "Mixer", "Norm", "PagedKVSpec", "Part",
            "PlanContext", "PositionEncoding", "StateSpec", "PreNormBlock", "OutputHead", "TokenEmbedding",
-           "SwiGLUFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding"]
+           "SwiGLUFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "DeltaRuleMixer", "ParallelMixer",
+           "PolyNormFeedForward", "RetentionMixer"]

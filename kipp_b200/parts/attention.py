@@ -5,6 +5,12 @@ Order of operations as the reference's block (docs/ARCHITECTURE.md:77-92,
 src/kipp.c:2950-2993): q/k/v projections (no bias) -> per-head norm of q and k
 -> rotation -> keys and values into the cache -> attention -> output
 projection added to the residual stream.  The part itself: csrc/host/parts.hpp.
+
+Options (each off by default): ``value_dim`` value heads of a size of their
+own; ``keep_first`` a window keeps the first positions of the sequence visible;
+``head_mix`` a tensor [heads, heads] mixes the heads' scores before the softmax;
+``output_scale`` a factor on the mixer's output; ``names`` the checkpoint names
+of its tensors by role (q, k, v, o, q_norm, k_norm, head_mix).
 """
 from __future__ import annotations
 
@@ -18,7 +24,9 @@ class AttentionMixer(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PositionEncoding, qk_norm_eps: Optional[float] = None,
-                 window: Optional[int] = None, scale: Optional[float] = None):
+                 window: Optional[int] = None, scale: Optional[float] = None, *,
+                 value_dim: Optional[int] = None, keep_first: int = 0, head_mix: bool = False,
+                 output_scale: float = 1.0, names: Optional[dict] = None):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden_size = hidden_size
@@ -31,11 +39,16 @@ class AttentionMixer(Mixer):
         self.scale = scale
         self.q_dim = num_heads * head_dim
         self.kv_dim = num_kv_heads * head_dim
+        self.value_dim, self.keep_first, self.head_mix = value_dim, keep_first, head_mix
+        self.output_scale, self.names = output_scale, dict(names or {})
 
     def cache_spec(self) -> PagedKVSpec:
-        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window, self.value_dim,
+                           self.keep_first if self.window else 0)
 
     def params(self, prefix, ctx) -> dict:
         return {"hidden_size": self.hidden_size, "num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads,
                 "head_dim": self.head_dim, "position": self.position.describe(prefix, ctx),
-                "qk_norm_eps": self.qk_norm_eps, "window": int(self.window or 0), "scale": self.scale}
+                "qk_norm_eps": self.qk_norm_eps, "window": int(self.window or 0), "scale": self.scale,
+                "value_dim": int(self.value_dim or 0), "keep_first": int(self.keep_first),
+                "head_mix": bool(self.head_mix), "output_scale": float(self.output_scale), "names": self.names}

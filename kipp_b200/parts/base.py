@@ -38,11 +38,15 @@ from ..weights.spec import TensorSpec
 class PagedKVSpec:
     """Cache need of a mixer: keys and values of ``kv_heads`` heads of
     ``head_dim`` per token.  ``window`` None keeps every key; a window of w
-    keeps keys j with pos - w < j <= pos.  Runs with equal specs share a group
-    of the cache manager (own pool, own block tables, own retention)."""
+    keeps keys j with pos - w < j <= pos and, beside them, the first
+    ``keep_first`` positions of the sequence.  ``value_dim`` None: values as wide
+    as keys.  Runs with equal specs share a group of the cache manager (own pool,
+    own block tables, own retention)."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    value_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclasses.dataclass(frozen=True)
