@@ -16,13 +16,20 @@
 // every sum depends on the token's own position only: not on how the prompt was
 // cut, on the batch, or on the pages.
 //
-// attention_mix_kernel: one block per token, any sizes, both element types.
+// attention_mix_kernel: one block per token (and, in steps of few tokens, per run of
+// SPLIT_TILES key tiles of that token: the runs' partial results -- maximum, sum and
+// unnormalised output per head -- are merged in run order by attention_mix_merge_kernel; how a
+// token's keys are cut into runs depends on its own position only).  Per tile the block gathers
+// the keys and values of every key/value head from the pages into shared memory with 16-byte
+// loads, forms all heads' scores from there, mixes and masks them, advances the softmax of each
+// head, and adds the weighted values.  Any sizes, both element types.
 #include "common.cuh"
 #include <math.h>
+#include <algorithm>
 
 namespace {
 constexpr int KT = 32;             // keys per tile
-constexpr int THREADS = 128;
+constexpr int THREADS = 256;
 
 template <typename T> struct Vec;
 template <> struct Vec<float> { static constexpr int N = 4; };
@@ -65,6 +72,34 @@ __device__ __forceinline__ void visible_runs(int pos, int window, int keep_first
     kept = min(keep_first, first);
 }
 
+constexpr int SPLIT_TILES = 4;     // key tiles per run when a step's tokens are cut into runs
+
+// Rows of `elems` elements from the pages into shared memory (row stride ld), 16 bytes at a time
+// where the sizes allow; rows of keys that are not visible become zeros.
+template <typename T>
+__device__ __forceinline__ void stage_rows(T* __restrict__ dst, int ld, const T* __restrict__ pages, int elems,
+                                           int n_kv, int page_size, const int* pg, const int* sl, bool vec) {
+    constexpr int VEC = Vec<T>::N;
+    if (vec) {
+        // asynchronous copies: every chunk of the tile is in flight at once (the caller waits)
+        const int chunks = elems / VEC;
+        for (int i = threadIdx.x; i < n_kv * KT * chunks; i += THREADS) {
+            const int c = i % chunks, jj = (i / chunks) % KT, g = i / (chunks * KT);
+            const bool ok = pg[jj] >= 0;
+            const T* src = ok ? pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * elems + c * VEC : pages;
+            cp_async16(smem_address(dst + ((size_t)g * KT + jj) * ld + c * VEC), src, ok ? 16 : 0);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n_kv * KT * elems; i += THREADS) {
+            const int c = i % elems, jj = (i / elems) % KT, g = i / (elems * KT);
+            dst[((size_t)g * KT + jj) * ld + c] =
+                pg[jj] >= 0 ? pages[(((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * elems + c] : from_f32<T>(0.f);
+        }
+    }
+}
+
+template <typename T> __host__ __device__ constexpr int row_pad() { return 16 / (int)sizeof(T); }   // 16 bytes: no bank conflicts between rows
+
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pages,
@@ -72,8 +107,9 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
                      const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                      const int* __restrict__ block_table, int table_width, int page_size, int n_q, int n_kv,
                      int head_dim, int v_dim, float scale, int window, int keep_first, float out_scale,
-                     int* __restrict__ status) {
-    extern __shared__ float smem[];
+                     int split, float* __restrict__ partial, int* __restrict__ status) {
+    extern __shared__ __align__(16) float smem[];
+    const int ldk = head_dim + row_pad<T>(), ldv = v_dim + row_pad<T>();
     float* qs = smem;                              // [n_q][head_dim]
     float* mix = qs + n_q * head_dim;              // [n_q][n_q]
     float* sraw = mix + n_q * n_q;                 // [n_q][KT]
@@ -84,14 +120,28 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
     float* corr = l_run + n_q;                     // [n_q]
     int* pg = reinterpret_cast<int*>(corr + n_q);  // [KT] page of key, -1 = not visible
     int* sl = pg + KT;                             // [KT] slot in page
+    const size_t head_floats = ((size_t)n_q * head_dim + (size_t)n_q * n_q + 2 * (size_t)n_q * KT + (size_t)n_q * v_dim +
+                                3 * (size_t)n_q + 2 * KT + 3) / 4 * 4;
+    T* ktile = reinterpret_cast<T*>(smem + head_floats);           // [n_kv][KT][ldk]
+    T* vtile = ktile + (size_t)n_kv * KT * ldk;                    // [n_kv][KT][ldv]
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t = blockIdx.x;
     const int pos = positions[t];
+    int first, kept;
+    visible_runs(pos, window, keep_first, first, kept);
+    const int kept_tiles = (kept + KT - 1) / KT;
+    const int win0 = first / KT;
+    const int n_tiles = kept_tiles + pos / KT - win0 + 1;
+    const int it0 = split ? blockIdx.y * SPLIT_TILES : 0;
+    if (it0 >= n_tiles) return;                    // this token has fewer runs than the step's longest
+    const int it1 = split ? min(n_tiles, it0 + SPLIT_TILES) : n_tiles;
     const int* table = block_table + (size_t)entry_of_token[t] * table_width;
     const int group = n_q / n_kv;
-    const bool kvec = head_dim % Vec<T>::N == 0 && (((uintptr_t)k_pages) & 15) == 0;
+    constexpr int VEC = Vec<T>::N;
+    const bool kvec = head_dim % VEC == 0 && (((uintptr_t)k_pages) & 15) == 0;
+    const bool vvec = v_dim % VEC == 0 && (((uintptr_t)v_pages) & 15) == 0;
 
     for (int i = tid; i < n_q * head_dim; i += THREADS) qs[i] = to_f32(q[(size_t)t * n_q * head_dim + i]);
     if (head_mix != nullptr)
@@ -99,12 +149,7 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
     for (int i = tid; i < n_q * v_dim; i += THREADS) acc[i] = 0.f;
     for (int i = tid; i < n_q; i += THREADS) { m_run[i] = -INFINITY; l_run[i] = 0.f; corr[i] = 1.f; }
 
-    int first, kept;
-    visible_runs(pos, window, keep_first, first, kept);
-    const int kept_tiles = (kept + KT - 1) / KT;
-    const int win0 = first / KT;
-    const int win_tiles = pos / KT - win0 + 1;
-    for (int it = 0; it < kept_tiles + win_tiles; ++it) {
+    for (int it = it0; it < it1; ++it) {
         const bool in_kept = it < kept_tiles;
         const int j0 = in_kept ? it * KT : (win0 + it - kept_tiles) * KT;
         const int lo = in_kept ? 0 : first, hi = in_kept ? kept : pos + 1;
@@ -120,14 +165,14 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
             sl[tid] = j % page_size;
         }
         __syncthreads();
+        stage_rows(ktile, ldk, k_pages, head_dim, n_kv, page_size, pg, sl, kvec);
+        stage_rows(vtile, ldv, v_pages, v_dim, n_kv, page_size, pg, sl, vvec);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
         for (int idx = tid; idx < n_q * KT; idx += THREADS) {
             const int h = idx / KT, jj = idx % KT;
-            float s = 0.f;
-            if (pg[jj] >= 0) {
-                const T* krow = k_pages + (((size_t)pg[jj] * n_kv + h / group) * page_size + sl[jj]) * head_dim;
-                s = dot_row(qs + h * head_dim, krow, head_dim, kvec) * scale;
-            }
-            sraw[idx] = s;
+            sraw[idx] = dot_row(qs + h * head_dim, ktile + ((size_t)(h / group) * KT + jj) * ldk, head_dim, kvec) * scale;
         }
         __syncthreads();
         for (int h = warp; h < n_q; h += THREADS / 32) {
@@ -156,64 +201,123 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
             }
         }
         __syncthreads();
+        // rows of keys that are not visible hold zeros and have weight zero: no branch
         for (int e = tid; e < n_q * v_dim; e += THREADS) {
             const int h = e / v_dim, d = e % v_dim;
-            float a = acc[e] * corr[h];
-            for (int jj = 0; jj < KT; ++jj) {
-                if (pg[jj] < 0) continue;
-                const T* vrow = v_pages + (((size_t)pg[jj] * n_kv + h / group) * page_size + sl[jj]) * v_dim;
-                a = fmaf(pw[h * KT + jj], to_f32(vrow[d]), a);
+            const T* vcol = vtile + (size_t)(h / group) * KT * ldv + d;
+            const float* ph = pw + h * KT;
+            float a0 = acc[e] * corr[h], a1 = 0.f;
+#pragma unroll 8
+            for (int jj = 0; jj < KT; jj += 2) {
+                a0 = fmaf(ph[jj], to_f32(vcol[(size_t)jj * ldv]), a0);
+                a1 = fmaf(ph[jj + 1], to_f32(vcol[(size_t)(jj + 1) * ldv]), a1);
             }
-            acc[e] = a;
+            acc[e] = a0 + a1;
         }
     }
     __syncthreads();
+    if (split) {
+        // this run's maximum, sum and unnormalised output per head: [token][run][head][2 + v_dim]
+        float* dst = partial + ((size_t)t * gridDim.y + blockIdx.y) * n_q * (v_dim + 2);
+        for (int e = tid; e < n_q * v_dim; e += THREADS) dst[(size_t)(e / v_dim) * (v_dim + 2) + 2 + e % v_dim] = acc[e];
+        for (int h = tid; h < n_q; h += THREADS) {
+            dst[(size_t)h * (v_dim + 2)] = m_run[h];
+            dst[(size_t)h * (v_dim + 2) + 1] = l_run[h];
+        }
+        return;
+    }
     for (int e = tid; e < n_q * v_dim; e += THREADS) {
         const float l = l_run[e / v_dim];
         out[(size_t)t * n_q * v_dim + e] = from_f32<T>(l > 0.f ? acc[e] / l * out_scale : 0.f);
     }
 }
 
+// The runs of a token merged in run order: o = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M).
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+attention_mix_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, const int* __restrict__ positions,
+                           int n_q, int v_dim, int window, int keep_first, int max_runs, float out_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, pos = positions[t];
+    int first, kept;
+    visible_runs(pos, window, keep_first, first, kept);
+    const int n_tiles = (kept + KT - 1) / KT + pos / KT - first / KT + 1;
+    const int runs = min(max_runs, (n_tiles + SPLIT_TILES - 1) / SPLIT_TILES);
+    const float* src = partial + (size_t)t * max_runs * n_q * (v_dim + 2);
+    for (int e = threadIdx.x; e < n_q * v_dim; e += THREADS) {
+        const int h = e / v_dim, d = e % v_dim;
+        float m = -INFINITY;
+        for (int r = 0; r < runs; ++r) m = fmaxf(m, src[((size_t)r * n_q + h) * (v_dim + 2)]);
+        float l = 0.f, o = 0.f;
+        for (int r = 0; r < runs; ++r) {
+            const float* p = src + ((size_t)r * n_q + h) * (v_dim + 2);
+            const float w = p[0] == -INFINITY ? 0.f : expf(p[0] - m);
+            l = fmaf(p[1], w, l);
+            o = fmaf(p[2 + d], w, o);
+        }
+        out[(size_t)t * n_q * v_dim + e] = from_f32<T>(l > 0.f ? o / l * out_scale : 0.f);
+    }
+}
+
+template <typename T>
+int launch_mix(void* out, const void* q, const void* k_pages, const void* v_pages, const float* head_mix,
+               const int* positions, const int* entry_of_token, const int* block_table, int table_width, int page_size,
+               int tokens, int n_q, int n_kv, int head_dim, int v_dim, float scale, int window, int keep_first,
+               float out_scale, int runs, float* partial, int* status, cudaStream_t s) {
+    const size_t head_floats = ((size_t)n_q * head_dim + (size_t)n_q * n_q + 2 * (size_t)n_q * KT + (size_t)n_q * v_dim +
+                                3 * (size_t)n_q + 2 * KT + 3) / 4 * 4;
+    const size_t smem = head_floats * sizeof(float) +
+                        (size_t)n_kv * KT * ((size_t)head_dim + v_dim + 2 * row_pad<T>()) * sizeof(T);
+    if (smem > 200 * 1024) return KIPP_ERR_ARG;
+    auto kernel = attention_mix_kernel<T>;
+    static size_t allowed = 0;
+    if (smem > 48 * 1024 && smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+        allowed = smem;
+    }
+    const int split = runs > 1 ? 1 : 0;
+    int rc = kipp_launch(kernel, dim3((unsigned)tokens, (unsigned)(split ? runs : 1)), dim3(THREADS), smem, s, 1, (T*)out,
+                         (const T*)q, (const T*)k_pages, (const T*)v_pages, head_mix, positions, entry_of_token,
+                         block_table, table_width, page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
+                         out_scale, split, partial, status);
+    if (rc || !split) return rc;
+    return kipp_launch(attention_mix_merge_kernel<T>, dim3((unsigned)tokens), dim3(THREADS), 0, s, 1, (T*)out,
+                       (const float*)partial, positions, n_q, v_dim, window, keep_first, runs, out_scale);
+}
 }  // namespace
+
+// Runs a step of `tokens` tokens is cut into (1: every token walks its keys in one block): few
+// tokens with many keys are cut so that the GPU has blocks to run.  max_keys bounds the context.
+extern "C" int kipp_attention_mix_runs(int tokens, int window, int keep_first, int max_keys) {
+    if (tokens <= 0 || tokens > 64) return 1;
+    const int win_tiles = window > 0 ? std::min((window - 1) / KT + 2, max_keys / KT + 1) : max_keys / KT + 1;
+    const int kept_tiles = window > 0 ? (std::min(keep_first, max_keys) + KT - 1) / KT : 0;
+    return std::max(1, (win_tiles + kept_tiles + SPLIT_TILES - 1) / SPLIT_TILES);
+}
+// float32 values of scratch a step cut into `runs` runs needs.
+extern "C" long long kipp_attention_mix_scratch_floats(int tokens, int runs, int n_q, int v_dim) {
+    return runs > 1 ? (long long)tokens * runs * n_q * (v_dim + 2) : 0;
+}
 
 extern "C" int kipp_attention_mix(void* out, const void* q, const void* k_pages, const void* v_pages, int dtype,
                                   const float* head_mix, const int* positions, const int* entry_of_token,
                                   const int* block_table, int table_width, int page_size, int tokens, int n_q,
                                   int n_kv, int head_dim, int v_dim, float scale, int window, int keep_first,
-                                  float out_scale, int* status, void* stream) {
+                                  float out_scale, int runs, float* partial, int* status, void* stream) {
     if (tokens <= 0) return 0;
     if (head_dim <= 0 || v_dim <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || page_size <= 0 || window < 0 ||
-        keep_first < 0)
+        keep_first < 0 || runs < 1 || (runs > 1 && partial == nullptr))
         return KIPP_ERR_ARG;
-    const size_t smem = ((size_t)n_q * head_dim + (size_t)n_q * n_q + 2 * (size_t)n_q * KT + (size_t)n_q * v_dim +
-                         3 * (size_t)n_q) * sizeof(float) + 2 * KT * sizeof(int);
-    if (smem > 200 * 1024) return KIPP_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == KIPP_DT_F32) {
-        auto kernel = attention_mix_kernel<float>;
-        static size_t allowed = 0;
-        if (smem > 48 * 1024 && smem > allowed) {
-            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-            allowed = smem;
-        }
-        return kipp_launch(kernel, dim3((unsigned)tokens), dim3(THREADS), smem, s, 1, (float*)out, (const float*)q,
-                           (const float*)k_pages, (const float*)v_pages, head_mix, positions, entry_of_token,
-                           block_table, table_width, page_size, n_q, n_kv, head_dim, v_dim, scale, window,
-                           keep_first, out_scale, status);
-    }
-    if (dtype == KIPP_DT_BF16) {
-        auto kernel = attention_mix_kernel<bf16>;
-        static size_t allowed = 0;
-        if (smem > 48 * 1024 && smem > allowed) {
-            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-            allowed = smem;
-        }
-        return kipp_launch(kernel, dim3((unsigned)tokens), dim3(THREADS), smem, s, 1, (bf16*)out, (const bf16*)q,
-                           (const bf16*)k_pages, (const bf16*)v_pages, head_mix, positions, entry_of_token,
-                           block_table, table_width, page_size, n_q, n_kv, head_dim, v_dim, scale, window,
-                           keep_first, out_scale, status);
-    }
+    if (dtype == KIPP_DT_F32)
+        return launch_mix<float>(out, q, k_pages, v_pages, head_mix, positions, entry_of_token, block_table, table_width,
+                                 page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, runs,
+                                 partial, status, s);
+    if (dtype == KIPP_DT_BF16)
+        return launch_mix<bf16>(out, q, k_pages, v_pages, head_mix, positions, entry_of_token, block_table, table_width,
+                                page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, runs,
+                                partial, status, s);
     return KIPP_ERR_DTYPE;
 }

@@ -220,12 +220,20 @@ public:
                        const int* positions, const int* entry_of_token, int tokens, int n_q, int n_kv, int head_dim,
                        int v_dim, float scale, int window, int keep_first, float out_scale) {
         using Fn = int (*)(void*, const void*, const void*, const void*, int, const float*, const int*, const int*,
-                           const int*, int, int, int, int, int, int, int, float, int, int, float, int*, void*);
+                           const int*, int, int, int, int, int, int, int, float, int, int, float, int, float*, int*, void*);
+        using Fr = int (*)(int, int, int, int);
+        using Fs = long long (*)(int, int, int, int);
         static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix");
+        static Fr runs_of = kernel_symbol<Fr>("attention_mix", "kipp_attention_mix_runs");
+        static Fs scratch_of = kernel_symbol<Fs>("attention_mix", "kipp_attention_mix_scratch_floats");
+        // a step of few tokens is cut into runs of keys (the table's width bounds the context)
+        const int runs = runs_of(tokens, window, keep_first, cache.table_width * cache.page_size);
+        float* partial = runs > 1 ? workspace->get<float>("attention_mix_runs", (size_t)scratch_of(tokens, runs, n_q, v_dim))
+                                  : nullptr;
         run(f(out, q, cache.k_pages, cache.v_pages, dtype, head_mix, positions, entry_of_token, cache.block_table,
               cache.table_width, cache.page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
-              out_scale, status, stream),
-            "attention_mix");
+              out_scale, runs, partial, status, stream),
+            "attention_mix", runs > 1 ? 2 : 1);
     }
 
     // Whether the recurrent scan kernels take heads of these sizes.
@@ -234,33 +242,41 @@ public:
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
         return f(dim, v_dim, delta ? 1 : 0) != 0;
     }
+    float* recurrent_scratch(int tokens, int heads, int dim, int v_dim, bool delta) {
+        using Fn = long long (*)(int, int, int, int, int);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scratch_floats");
+        return workspace->get<float>("recurrent_scratch", (size_t)f(tokens, heads, dim, v_dim, delta ? 1 : 0));
+    }
     // S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t over each entry's tokens, from the state in
     // its slot and back into it; q and k rotated by the step's table and k scaled; then per-head
     // root-mean-square division, gate (1 silu, 2 sigmoid of the g columns), out_scale.
     void retention_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int q_off,
                         int k_off, int v_off, int g_off, float* state, const float* decay, const float* cos_sin,
-                        int rot, const int* q_start, const int* slots, int entries, int heads, int dim, int v_dim,
-                        float k_scale, float eps, float out_scale, int gate) {
+                        int rot, const int* q_start, const int* slots, int entries, int tokens, int heads, int dim,
+                        int v_dim, float k_scale, float eps, float out_scale, int gate) {
         using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, float*, const float*,
-                           const float*, int, const int*, const int*, int, int, int, int, float, float, float, int, void*);
+                           const float*, int, const int*, const int*, int, int, int, int, int, float, float, float, int,
+                           float*, void*);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_retention_scan");
+        float* scratch = recurrent_scratch(tokens, heads, dim, v_dim, false);
         run(f(out, ld_out, proj, ld_proj, dtype, q_off, k_off, v_off, g_off, state, decay, cos_sin, rot, q_start, slots,
-              entries, heads, dim, v_dim, k_scale, eps, out_scale, gate, stream),
-            "retention_scan");
+              entries, tokens, heads, dim, v_dim, k_scale, eps, out_scale, gate, scratch, stream),
+            "retention_scan", 3);
     }
     // S_t = diag(w_t) S_{t-1} - (a_t u_t)(u_t^T S_{t-1}) + k_t v_t^T, o_t = S_t^T r_t (see recurrent.cu).
     void delta_rule_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int r_off,
                          int k_off, int v_off, int g_off, int a_off, const void* w_raw, long long ld_w,
                          const float* a_bias, const float* w_bias, const float* norm_w, float* state,
-                         const int* q_start, const int* slots, int entries, int heads, int dim, float eps,
-                         float out_scale, int gate) {
+                         const int* q_start, const int* slots, int entries, int tokens, int heads, int dim,
+                         float eps, float out_scale, int gate) {
         using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, int, const void*, long long,
-                           const float*, const float*, const float*, float*, const int*, const int*, int, int, int,
-                           float, float, int, void*);
+                           const float*, const float*, const float*, float*, const int*, const int*, int, int, int, int,
+                           float, float, int, float*, void*);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_delta_rule_scan");
+        float* scratch = recurrent_scratch(tokens, heads, dim, dim, true);
         run(f(out, ld_out, proj, ld_proj, dtype, r_off, k_off, v_off, g_off, a_off, w_raw, ld_w, a_bias, w_bias, norm_w,
-              state, q_start, slots, entries, heads, dim, eps, out_scale, gate, stream),
-            "delta_rule_scan");
+              state, q_start, slots, entries, tokens, heads, dim, eps, out_scale, gate, scratch, stream),
+            "delta_rule_scan", 3);
     }
     void tanh_rows(void* out, long long ld_out, const void* in, long long ld_in, int dtype, int rows, int cols) {
         using Fn = int (*)(void*, long long, const void*, long long, int, int, int, void*);

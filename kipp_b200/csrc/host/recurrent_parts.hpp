@@ -108,7 +108,7 @@ public:
         float* state = static_cast<float*>(ctx.state_view(run, mixer_slot, nullptr));
         void* gated = ctx.workspace->buffer("retention_out", (size_t)T * vv_ * es);
         ops.retention_scan(gated, vv_, proj, cols_, ctx.dtype, 0, qk_, 2 * qk_, 2 * qk_ + vv_, state, decay_dev_, cos_sin,
-                           position_->rotary_dim(), m.q_start, m.slots, m.shape.entries, heads_, dim_, v_dim_,
+                           position_->rotary_dim(), m.q_start, m.slots, m.shape.entries, T, heads_, dim_, v_dim_,
                            key_scale_, eps_, out_scale_, gate_);
         const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
         ops.gemm(residual, F32, hidden_, gated, vv_, w_o_, vv_, dtype_, T, hidden_, vv_, EPI_ADD, emit);
@@ -236,7 +236,7 @@ public:
         float* state = static_cast<float*>(ctx.state_view(run, mixer_slot, nullptr));
         void* gated = ctx.workspace->buffer("delta_out", (size_t)T * hd_ * es);
         ops.delta_rule_scan(gated, hd_, proj, ld_, ctx.dtype, 0, hd_, 2 * hd_, g_off, a_off, w_raw, hd_, a_bias_, w_bias_,
-                            norm_, state, m.q_start, m.slots, m.shape.entries, heads_, dim_, eps_, out_scale_, gate_);
+                            norm_, state, m.q_start, m.slots, m.shape.entries, T, heads_, dim_, eps_, out_scale_, gate_);
         const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
         ops.gemm(residual, F32, hidden_, gated, hd_, w_o_, hd_, dtype_, T, hidden_, hd_, EPI_ADD, emit);
         fold_emitted(ctx, emit, hidden_);

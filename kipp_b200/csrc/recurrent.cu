@@ -18,14 +18,16 @@
 // Everything that enters the recurrence is formed in float32 from the
 // projections (which arrive in the compute type); the state never leaves float32.
 //
-// One block per (entry, head).  A thread owns one value column of S and a run of
-// at most 32 key rows (P = 1, 2, 4 or 8 threads per column, neighbours in a
-// warp, their partial sums met by shuffles).  Tokens are taken in batches:
-// the block first forms the batch's per-token vectors in shared memory (a warp
-// per token), then every thread walks the batch with its part of the state in
-// registers, then a warp per token norms, gates and stores.  The state is read
-// from and written back to its slot once per launch; a decoded token is a batch
-// of one.  The order of every sum depends on the sizes only.
+// Three kernels per step.  (1) prepare: a warp per (token, head) forms the token's vectors in
+// float32 (q/r, k, and for the delta rule w, a * u, u) in a workspace; fully parallel over the
+// step's tokens.  (2) scan: a block per (entry, head, slice of 32 value columns) -- the columns
+// of S evolve independently -- walks the entry's tokens in order; a thread owns one column and a
+// run of at most 32 key rows in registers (P = 1, 2, 4 or 8 threads per column, neighbours in a
+// warp, their partial sums met by shuffles); the token vectors come through shared memory in
+// batches.  The state is read from and written back to its slot once per launch; a decoded token
+// is a batch of one.  (3) finish: a warp per (token, head) divides by the root mean square,
+// applies weight, gate and scale and stores in the compute type.  The order of every sum depends
+// on the sizes only.
 #include "common.cuh"
 #include <math.h>
 #include <algorithm>
@@ -52,170 +54,240 @@ struct ScanArgs {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-template <typename T, bool DELTA, int P, int MAXT>
-__global__ void __launch_bounds__(MAXT)
-recurrent_scan_kernel(const ScanArgs a) {
-    extern __shared__ float smem[];
-    const int D = a.dim, V = a.v_dim, TB = a.batch;
-    float* rq = smem;                      // [TB][D] query / receptance
-    float* kk = rq + TB * D;               // [TB][D]
-    float* vv = kk + TB * D;               // [TB][V]
-    float* ob = vv + TB * V;               // [TB][V]
-    float* ww = ob + TB * V;               // delta: [TB][D] decay
-    float* au = ww + (DELTA ? TB * D : 0); // delta: [TB][D] a * u
-    float* uu = au + (DELTA ? TB * D : 0); // delta: [TB][D] unit key
+// (1) the token vectors: one record of NV * D + V floats per (head, token), heads outermost so that
+// a head's consecutive tokens are neighbours: NV = 5 (delta: r, k, w, a*u, u) or 2 (q, k), then v
+template <typename T, bool DELTA>
+__global__ void __launch_bounds__(128)
+recurrent_prepare_kernel(const ScanArgs a, float* __restrict__ vec, int tokens) {
     pdl_launch_dependents();
     pdl_wait();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
-    const int e = blockIdx.x / a.heads, h = blockIdx.x % a.heads;
+    constexpr int NV = DELTA ? 5 : 2;
+    const int lane = threadIdx.x & 31;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)tokens * a.heads) return;
+    const size_t row = (size_t)(wg / a.heads);
+    const int h = (int)(wg % a.heads), D = a.dim;
+    const T* pr = static_cast<const T*>(a.proj) + row * a.ld_proj;
+    const int rec = NV * D + a.v_dim;
+    float* dst = vec + ((size_t)h * tokens + row) * rec;
+    for (int c = lane; c < a.v_dim; c += 32) dst[NV * D + c] = to_f32(pr[a.v_off + h * a.v_dim + c]);
+    if (DELTA) {
+        const T* w_raw = static_cast<const T*>(a.w_raw);
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float k = to_f32(pr[a.k_off + h * D + d]);
+            ss = fmaf(k, k, ss);
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss + 1e-6f);
+        for (int d = lane; d < D; d += 32) {
+            const int c = h * D + d;
+            const float k = to_f32(pr[a.k_off + c]);
+            const float u = k * inv;
+            const float rate = sigmoidf_(to_f32(pr[a.a_off + c]) + a.a_bias[c]);
+            const float wr = to_f32(w_raw[row * a.ld_w + c]) + a.w_bias[c];
+            dst[d] = to_f32(pr[a.q_off + c]);
+            dst[D + d] = k;
+            dst[2 * D + d] = expf(-0.6065306597126334f * sigmoidf_(wr));
+            dst[3 * D + d] = rate * u;
+            dst[4 * D + d] = u;
+        }
+    } else {
+        const int half = a.rot / 2;
+        const float2* cs = a.cos_sin ? reinterpret_cast<const float2*>(a.cos_sin) + row * half : nullptr;
+        for (int d = lane; d < D; d += 32) {
+            const int c = h * D + d;
+            float q = to_f32(pr[a.q_off + c]), k = to_f32(pr[a.k_off + c]);
+            if (cs != nullptr && d < a.rot) {
+                const bool low = d < half;
+                const float2 t = cs[low ? d : d - half];
+                const float q2 = to_f32(pr[a.q_off + h * D + (low ? d + half : d - half)]);
+                const float k2 = to_f32(pr[a.k_off + h * D + (low ? d + half : d - half)]);
+                // low: u cos - v sin; high: v cos + u sin (u the low half, v the high one)
+                q = low ? q * t.x - q2 * t.y : q * t.x + q2 * t.y;
+                k = low ? k * t.x - k2 * t.y : k * t.x + k2 * t.y;
+            }
+            dst[d] = q;
+            dst[D + d] = k * a.k_scale;
+        }
+    }
+}
+
+// (2) the recurrence; raw o goes to o_raw [T, heads * v_dim] float32.  The records of a batch of
+// tokens come into shared memory by asynchronous copies, the next batch while this one is walked.
+constexpr int VS = 32;                     // value columns per block
+template <bool DELTA>
+__device__ __forceinline__ void load_batch(float* __restrict__ tv, float* __restrict__ vv, const float* __restrict__ rec0,
+                                           int rec, int nvd, int nb, int slice, int V, bool async, int threads) {
+    // rec0: the record of the batch's first token; the vectors' part [nvd] and this slice's values
+    if (async) {
+        const int c4 = nvd / 4;
+        for (int i = threadIdx.x; i < nb * c4; i += threads) {
+            const int tt = i / c4, c = i % c4;
+            cp_async16(smem_address(tv + (size_t)tt * nvd + c * 4), rec0 + (size_t)tt * rec + c * 4, 16);
+        }
+        for (int i = threadIdx.x; i < nb * (VS / 4); i += threads) {
+            const int tt = i / (VS / 4), c = i % (VS / 4), col = slice * VS + c * 4;
+            const bool ok = col < V;                    // V is a multiple of 4 here: a chunk is whole or absent
+            cp_async16(smem_address(vv + (size_t)tt * VS + c * 4), ok ? rec0 + (size_t)tt * rec + nvd + col : rec0, ok ? 16 : 0);
+        }
+    } else {
+        for (int i = threadIdx.x; i < nb * nvd; i += threads) tv[i] = rec0[(size_t)(i / nvd) * rec + i % nvd];
+        for (int i = threadIdx.x; i < nb * VS; i += threads) {
+            const int col = slice * VS + i % VS;
+            vv[i] = col < V ? rec0[(size_t)(i / VS) * rec + nvd + col] : 0.f;
+        }
+    }
+    cp_async_commit();
+}
+
+template <typename T, bool DELTA, int P, int CHUNK>
+__global__ void __launch_bounds__(VS * P)
+recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __restrict__ o_raw, int v_slices,
+                      int tokens) {
+    extern __shared__ __align__(16) float smem[];
+    constexpr int NV = DELTA ? 5 : 2;
+    const int D = a.dim, V = a.v_dim, TB = a.batch;
+    const int nvd = NV * D, rec = nvd + V;
+    float* tv[2] = {smem, smem + (size_t)TB * (nvd + VS)};      // [TB][NV][D] twice
+    float* vv[2] = {tv[0] + (size_t)TB * nvd, tv[1] + (size_t)TB * nvd};   // [TB][VS] twice
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x;
+    const int slice = blockIdx.x % v_slices, eh = blockIdx.x / v_slices;
+    const int e = eh / a.heads, h = eh % a.heads;
     const int row0 = a.q_start[e], n_tok = a.q_start[e + 1] - row0;
-    const int p = tid % P, col = tid / P;
-    const int chunk = (D + P - 1) / P, d0 = p * chunk;
+    const int p = tid % P, cl = tid / P, col = slice * VS + cl;
+    const int d0 = p * CHUNK;
     const bool live = col < V;
     float* S_slot = a.state + ((size_t)a.slots[e] * a.heads + h) * (size_t)D * V;
-    const T* proj = static_cast<const T*>(a.proj);
-    const T* w_raw = static_cast<const T*>(a.w_raw);
-    T* out = static_cast<T*>(a.out);
+    const float* recs = vec + ((size_t)h * tokens + row0) * rec;
+    // 16-byte copies need every record and every part of it on a 16-byte boundary
+    const bool async = nvd % 4 == 0 && V % 4 == 0;
 
-    float S[MAX_CHUNK];
+    float S[CHUNK];
 #pragma unroll
-    for (int i = 0; i < MAX_CHUNK; ++i) S[i] = (live && i < chunk && d0 + i < D) ? S_slot[(size_t)(d0 + i) * V + col] : 0.f;
+    for (int i = 0; i < CHUNK; ++i) S[i] = (live && d0 + i < D) ? S_slot[(size_t)(d0 + i) * V + col] : 0.f;
     const float decay = DELTA ? 0.f : a.decay[h];
-    const int half = a.rot / 2;
 
-    for (int t0 = 0; t0 < n_tok; t0 += TB) {
+    load_batch<DELTA>(tv[0], vv[0], recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
+    int buf = 0;
+    for (int t0 = 0; t0 < n_tok; t0 += TB, buf ^= 1) {
         const int nb = min(TB, n_tok - t0);
+        if (t0 + TB < n_tok)
+            load_batch<DELTA>(tv[buf ^ 1], vv[buf ^ 1], recs + (size_t)(t0 + TB) * rec, rec, nvd, min(TB, n_tok - t0 - TB),
+                              slice, V, async, VS * P);
+        else
+            cp_async_commit();
+        cp_async_wait<1>();                 // this batch has landed; the next one may still be on its way
         __syncthreads();
-        // ---- the batch's vectors, a warp per token
-        for (int tt = warp; tt < nb; tt += n_warps) {
-            const size_t row = (size_t)(row0 + t0 + tt);
-            const T* pr = proj + row * a.ld_proj;
-            if (DELTA) {
-                float ss = 0.f;
-                for (int d = lane; d < D; d += 32) {
-                    const float k = to_f32(pr[a.k_off + h * D + d]);
-                    ss = fmaf(k, k, ss);
-                }
-                ss = warp_sum(ss);
-                const float inv = 1.0f / sqrtf(ss + 1e-6f);
-                for (int d = lane; d < D; d += 32) {
-                    const int c = h * D + d;
-                    const float k = to_f32(pr[a.k_off + c]);
-                    const float u = k * inv;
-                    const float rate = sigmoidf_(to_f32(pr[a.a_off + c]) + a.a_bias[c]);
-                    const float wr = to_f32(w_raw[row * a.ld_w + c]) + a.w_bias[c];
-                    rq[tt * D + d] = to_f32(pr[a.q_off + c]);
-                    kk[tt * D + d] = k;
-                    uu[tt * D + d] = u;
-                    au[tt * D + d] = rate * u;
-                    ww[tt * D + d] = expf(-0.6065306597126334f * sigmoidf_(wr));
-                }
-            } else {
-                const float2* cs = a.cos_sin ? reinterpret_cast<const float2*>(a.cos_sin) + row * half : nullptr;
-                for (int d = lane; d < D; d += 32) {
-                    const int c = h * D + d;
-                    float q = to_f32(pr[a.q_off + c]), k = to_f32(pr[a.k_off + c]);
-                    if (cs != nullptr && d < a.rot) {
-                        const bool low = d < half;
-                        const int i = low ? d : d - half;
-                        const float2 t = cs[i];
-                        const float q2 = to_f32(pr[a.q_off + h * D + (low ? d + half : d - half)]);
-                        const float k2 = to_f32(pr[a.k_off + h * D + (low ? d + half : d - half)]);
-                        // low: u cos - v sin; high: v cos + u sin (u the low half, v the high one)
-                        q = low ? q * t.x - q2 * t.y : q * t.x + q2 * t.y;
-                        k = low ? k * t.x - k2 * t.y : k * t.x + k2 * t.y;
-                    }
-                    rq[tt * D + d] = q;
-                    kk[tt * D + d] = k * a.k_scale;
-                }
-            }
-            for (int c = lane; c < V; c += 32) vv[tt * V + c] = to_f32(pr[a.v_off + h * V + c]);
-        }
-        __syncthreads();
-        // ---- the recurrence over the batch
+        const float* tvb = tv[buf];
+        const float* vvb = vv[buf];
         for (int tt = 0; tt < nb; ++tt) {
-            const float v = live ? vv[tt * V + col] : 0.f;
-            const float* kt = kk + tt * D + d0;
-            const float* qt = rq + tt * D + d0;
+            const float v = vvb[tt * VS + cl];
+            const float* base = tvb + tt * nvd + d0;
             float us = 0.f;
             if (DELTA) {
-                const float* ut = uu + tt * D + d0;
 #pragma unroll
-                for (int i = 0; i < MAX_CHUNK; ++i)
-                    if (i < chunk && d0 + i < D) us = fmaf(ut[i], S[i], us);
+                for (int i = 0; i < CHUNK; ++i)
+                    if (d0 + i < D) us = fmaf(base[4 * D + i], S[i], us);
 #pragma unroll
-                for (int o = P / 2; o > 0; o >>= 1) us += __shfl_xor_sync(0xffffffffu, us, o);
+                for (int x = P / 2; x > 0; x >>= 1) us += __shfl_xor_sync(0xffffffffu, us, x);
             }
             float o = 0.f;
 #pragma unroll
-            for (int i = 0; i < MAX_CHUNK; ++i) {
-                if (i < chunk && d0 + i < D) {
+            for (int i = 0; i < CHUNK; ++i) {
+                if (d0 + i < D) {
                     float s;
-                    if (DELTA) s = fmaf(kt[i], v, fmaf(-(au + tt * D + d0)[i], us, (ww + tt * D + d0)[i] * S[i]));
-                    else s = fmaf(kt[i], v, decay * S[i]);
+                    if (DELTA) s = fmaf(base[D + i], v, fmaf(-base[3 * D + i], us, base[2 * D + i] * S[i]));
+                    else s = fmaf(base[D + i], v, decay * S[i]);
                     S[i] = s;
-                    o = fmaf(s, qt[i], o);
+                    o = fmaf(s, base[i], o);
                 }
             }
 #pragma unroll
             for (int x = P / 2; x > 0; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
-            if (live && p == 0) ob[tt * V + col] = o;
+            if (live && p == 0) o_raw[(size_t)(row0 + t0 + tt) * (a.heads * V) + h * V + col] = o;
         }
-        __syncthreads();
-        // ---- per-head norm, gate, store: a warp per token
-        for (int tt = warp; tt < nb; tt += n_warps) {
-            const size_t row = (size_t)(row0 + t0 + tt);
-            float ss = 0.f;
-            for (int c = lane; c < V; c += 32) ss = fmaf(ob[tt * V + c], ob[tt * V + c], ss);
-            ss = warp_sum(ss);
-            const float inv = 1.0f / sqrtf(ss / (float)V + a.eps);
-            for (int c = lane; c < V; c += 32) {
-                const int hc = h * V + c;
-                float y = ob[tt * V + c] * inv;
-                if (a.norm_w != nullptr) y *= a.norm_w[hc];
-                if (a.gate != 0) {
-                    const float g = to_f32(proj[row * a.ld_proj + a.g_off + hc]);
-                    y *= a.gate == 1 ? g * sigmoidf_(g) : sigmoidf_(g);
-                }
-                out[row * a.ld_out + hc] = from_f32<T>(y * a.out_scale);
-            }
-        }
+        __syncthreads();                    // the buffer is free for the batch after the next
     }
 #pragma unroll
-    for (int i = 0; i < MAX_CHUNK; ++i)
-        if (live && i < chunk && d0 + i < D) S_slot[(size_t)(d0 + i) * V + col] = S[i];
+    for (int i = 0; i < CHUNK; ++i)
+        if (live && d0 + i < D) S_slot[(size_t)(d0 + i) * V + col] = S[i];
 }
 
+// (3) per-head root-mean-square division, weight, gate, scale
+template <typename T>
+__global__ void __launch_bounds__(128)
+recurrent_finish_kernel(const ScanArgs a, const float* __restrict__ o_raw, int tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)tokens * a.heads) return;
+    const size_t row = (size_t)(wg / a.heads);
+    const int h = (int)(wg % a.heads), V = a.v_dim;
+    const float* o = o_raw + row * (a.heads * V) + h * V;
+    const T* proj = static_cast<const T*>(a.proj);
+    T* out = static_cast<T*>(a.out);
+    float ss = 0.f;
+    for (int c = lane; c < V; c += 32) ss = fmaf(o[c], o[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + a.eps);
+    for (int c = lane; c < V; c += 32) {
+        const int hc = h * V + c;
+        float y = o[c] * inv;
+        if (a.norm_w != nullptr) y *= a.norm_w[hc];
+        if (a.gate != 0) {
+            const float g = to_f32(proj[row * a.ld_proj + a.g_off + hc]);
+            y *= a.gate == 1 ? g * sigmoidf_(g) : sigmoidf_(g);
+        }
+        out[row * a.ld_out + hc] = from_f32<T>(y * a.out_scale);
+    }
+}
+
+template <typename T, bool DELTA, int P>
+int launch_scan_chunk(const ScanArgs& b, const float* vec, float* o_raw, int slices, int tokens, dim3 grid, size_t smem,
+                      cudaStream_t stream) {
+    const int chunk = (b.dim + P - 1) / P;
+    if (chunk <= 8) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 8>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+    if (chunk <= 16) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 16>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+    if (chunk <= 24) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 24>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+    return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 32>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+}
+
+// scratch: float32 [heads][tokens][NV * dim + v_dim] for the records, then [tokens][heads * v_dim] for raw o
 template <typename T, bool DELTA>
-int launch_scan(const ScanArgs& a, int entries, cudaStream_t stream) {
+int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cudaStream_t stream) {
     const int D = a.dim, V = a.v_dim;
+    constexpr int NV = DELTA ? 5 : 2;
+    // threads per column: runs of 8 key rows where the head allows (short chains of dependent
+    // multiply-adds, more warps per block), at most 8 threads
     int P = 1;
-    while ((D + P - 1) / P > MAX_CHUNK) P *= 2;
-    if (P > 8) return KIPP_ERR_ARG;
-    const int threads = (V * P + 31) / 32 * 32;
-    if (threads > 1024) return KIPP_ERR_ARG;
-    const size_t per_token = ((DELTA ? 5 : 2) * (size_t)D + 2 * (size_t)V) * sizeof(float);
-    int batch = (int)std::min<size_t>(16, (48 * 1024) / per_token);
+    while (P < 8 && (D + P - 1) / P > 8) P *= 2;
+    if ((D + P - 1) / P > MAX_CHUNK || scratch == nullptr) return KIPP_ERR_ARG;
+    const size_t per_token = ((size_t)NV * D + VS) * sizeof(float);
+    int batch = (int)std::min<size_t>(32, (20 * 1024) / per_token);       // two buffers of at most 20 KB
     if (batch < 1) return KIPP_ERR_ARG;
     ScanArgs b = a;
     b.batch = batch;
-    const size_t smem = per_token * batch;
-    const dim3 grid((unsigned)(entries * a.heads));
-    // up to 256 threads the compiler may use every register for the state; wider blocks spill a little
-    if (threads <= 256) {
-        switch (P) {
-        case 1: return kipp_launch(recurrent_scan_kernel<T, DELTA, 1, 256>, grid, dim3(threads), smem, stream, 1, b);
-        case 2: return kipp_launch(recurrent_scan_kernel<T, DELTA, 2, 256>, grid, dim3(threads), smem, stream, 1, b);
-        case 4: return kipp_launch(recurrent_scan_kernel<T, DELTA, 4, 256>, grid, dim3(threads), smem, stream, 1, b);
-        default: return kipp_launch(recurrent_scan_kernel<T, DELTA, 8, 256>, grid, dim3(threads), smem, stream, 1, b);
-        }
-    }
+    float* vec = scratch;
+    float* o_raw = scratch + (size_t)tokens * a.heads * (NV * D + V);
+    const long long warps = (long long)tokens * a.heads;
+    const dim3 wgrid((unsigned)((warps + 3) / 4));
+    int rc = kipp_launch(recurrent_prepare_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens);
+    if (rc) return rc;
+    const int slices = (V + VS - 1) / VS;
+    const dim3 grid((unsigned)(entries * a.heads * slices));
+    const size_t smem = 2 * per_token * batch;
     switch (P) {
-    case 1: return kipp_launch(recurrent_scan_kernel<T, DELTA, 1, 1024>, grid, dim3(threads), smem, stream, 1, b);
-    case 2: return kipp_launch(recurrent_scan_kernel<T, DELTA, 2, 1024>, grid, dim3(threads), smem, stream, 1, b);
-    case 4: return kipp_launch(recurrent_scan_kernel<T, DELTA, 4, 1024>, grid, dim3(threads), smem, stream, 1, b);
-    default: return kipp_launch(recurrent_scan_kernel<T, DELTA, 8, 1024>, grid, dim3(threads), smem, stream, 1, b);
+    case 1: rc = launch_scan_chunk<T, DELTA, 1>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
+    case 2: rc = launch_scan_chunk<T, DELTA, 2>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
+    case 4: rc = launch_scan_chunk<T, DELTA, 4>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
+    default: rc = launch_scan_chunk<T, DELTA, 8>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
     }
+    if (rc) return rc;
+    return kipp_launch(recurrent_finish_kernel<T>, wgrid, dim3(128), 0, stream, 1, b, (const float*)o_raw, tokens);
 }
 
 template <typename T>
@@ -233,18 +305,19 @@ __global__ void tanh_rows_kernel(T* __restrict__ out, long long ld_out, const T*
 // Whether the scan kernels take a head of these sizes.
 extern "C" int kipp_recurrent_scan_ok(int dim, int v_dim, int delta) {
     if (dim <= 0 || v_dim <= 0 || dim > 8 * MAX_CHUNK) return 0;
-    int P = 1;
-    while ((dim + P - 1) / P > MAX_CHUNK) P *= 2;
-    if ((v_dim * P + 31) / 32 * 32 > 1024) return 0;
-    return (((delta ? 5 : 2) * (size_t)dim + 2 * (size_t)v_dim) * sizeof(float)) <= 48 * 1024 ? 1 : 0;
+    return (((delta ? 5 : 2) * (size_t)dim + VS) * sizeof(float)) <= 20 * 1024 ? 1 : 0;
+}
+// float32 values of scratch a scan of `tokens` tokens needs.
+extern "C" long long kipp_recurrent_scratch_floats(int tokens, int heads, int dim, int v_dim, int delta) {
+    return (long long)tokens * heads * ((delta ? 5 : 2) * (long long)dim + 2 * (long long)v_dim);
 }
 
 extern "C" int kipp_retention_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype,
                                    int q_off, int k_off, int v_off, int g_off, float* state, const float* decay,
                                    const float* cos_sin, int rot, const int* q_start, const int* slots, int entries,
-                                   int heads, int dim, int v_dim, float k_scale, float eps, float out_scale,
-                                   int gate, void* stream) {
-    if (entries <= 0) return 0;
+                                   int tokens, int heads, int dim, int v_dim, float k_scale, float eps,
+                                   float out_scale, int gate, float* scratch, void* stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
     if (!kipp_recurrent_scan_ok(dim, v_dim, 0) || heads <= 0 || rot < 0 || rot > dim || (rot & 1)) return KIPP_ERR_ARG;
     ScanArgs a = {};
     a.out = out; a.ld_out = ld_out; a.proj = proj; a.ld_proj = ld_proj;
@@ -252,17 +325,18 @@ extern "C" int kipp_retention_scan(void* out, long long ld_out, const void* proj
     a.decay = decay; a.cos_sin = rot > 0 ? cos_sin : nullptr; a.rot = rot; a.state = state;
     a.q_start = q_start; a.slots = slots; a.heads = heads; a.dim = dim; a.v_dim = v_dim;
     a.k_scale = k_scale; a.eps = eps; a.out_scale = out_scale; a.gate = gate;
-    if (dtype == KIPP_DT_F32) return launch_scan<float, false>(a, entries, (cudaStream_t)stream);
-    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, false>(a, entries, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_F32) return launch_scan<float, false>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, false>(a, entries, tokens, scratch, (cudaStream_t)stream);
     return KIPP_ERR_DTYPE;
 }
 
 extern "C" int kipp_delta_rule_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype,
                                     int r_off, int k_off, int v_off, int g_off, int a_off, const void* w_raw,
                                     long long ld_w, const float* a_bias, const float* w_bias, const float* norm_w,
-                                    float* state, const int* q_start, const int* slots, int entries, int heads,
-                                    int dim, float eps, float out_scale, int gate, void* stream) {
-    if (entries <= 0) return 0;
+                                    float* state, const int* q_start, const int* slots, int entries, int tokens,
+                                    int heads, int dim, float eps, float out_scale, int gate, float* scratch,
+                                    void* stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
     if (!kipp_recurrent_scan_ok(dim, dim, 1) || heads <= 0 || a_bias == nullptr || w_bias == nullptr)
         return KIPP_ERR_ARG;
     ScanArgs a = {};
@@ -271,8 +345,8 @@ extern "C" int kipp_delta_rule_scan(void* out, long long ld_out, const void* pro
     a.w_raw = w_raw; a.ld_w = ld_w; a.a_bias = a_bias; a.w_bias = w_bias; a.norm_w = norm_w;
     a.state = state; a.q_start = q_start; a.slots = slots; a.heads = heads; a.dim = dim; a.v_dim = dim;
     a.k_scale = 1.f; a.eps = eps; a.out_scale = out_scale; a.gate = gate;
-    if (dtype == KIPP_DT_F32) return launch_scan<float, true>(a, entries, (cudaStream_t)stream);
-    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, true>(a, entries, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_F32) return launch_scan<float, true>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, true>(a, entries, tokens, scratch, (cudaStream_t)stream);
     return KIPP_ERR_DTYPE;
 }
 
