@@ -286,7 +286,313 @@ int launch_mix(void* out, const void* q, const void* k_pages, const void* v_page
     return kipp_launch(attention_mix_merge_kernel<T>, dim3((unsigned)tokens), dim3(THREADS), 0, s, 1, (T*)out,
                        (const float*)partial, positions, n_q, v_dim, window, keep_first, runs, out_scale);
 }
+
+// ---------------------------------------------------------------------------
+// Prompt portions in bfloat16 on the tensor cores (mma.sync m16n8k16).  A block of 8 warps
+// takes 8 consecutive queries of one entry (work item = (entry, first token)) and ALL heads.  The
+// products are formed transposed so that the 8 queries are the instruction's N: per tile of 32
+// keys  S^T[key][query] = K Q^T  for every head (keys as M, head_dim as K), the scores go to
+// shared memory in float32, are mixed over the heads and masked per (query, key), each (head,
+// query) row takes its softmax step in a warp (lane = key), and  O^T[value dim][query] +=
+// V^T P^T  (value dims as M, keys as K) adds to accumulators that stay in the registers of the
+// warp that owns the head.  The weights P keep float32 precision through the 16-bit product:
+// P = hi + lo with hi = bf16(P), lo = bf16(P - hi), two products into the same accumulator.
+// K and V tiles share one buffer: V is fetched (asynchronously) while the softmax runs.
+constexpr int QB = 8;
+constexpr int MMA_THREADS = 256;
+
+__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+struct MmaSmem {
+    int ldq, ldkv, lds, ldp;
+    size_t qs, kv, phi, plo, sraw, mix, m_run, l_run, corr, pg, bytes;     // byte offsets
+    __host__ __device__ MmaSmem(int n_q, int n_kv, int head_dim, int v_dim) {
+        ldq = head_dim + 8;
+        ldkv = (head_dim > v_dim ? head_dim : v_dim) + 8;
+        lds = KT + 1;
+        ldp = KT + 8;
+        size_t at = 0;
+        qs = at; at += (size_t)n_q * QB * ldq * 2;
+        kv = at; at += (size_t)n_kv * KT * ldkv * 2;
+        phi = at; at += (size_t)n_q * QB * ldp * 2;
+        plo = at; at += (size_t)n_q * QB * ldp * 2;
+        sraw = at; at += (size_t)n_q * QB * lds * 4;
+        mix = at; at += (size_t)n_q * n_q * 4;
+        m_run = at; at += (size_t)n_q * QB * 4;
+        l_run = at; at += (size_t)n_q * QB * 4;
+        corr = at; at += (size_t)n_q * QB * 4;
+        pg = at; at += 2 * KT * 4;
+        bytes = at;
+    }
+};
+
+template <int HPW, int VB>
+__global__ void __launch_bounds__(MMA_THREADS)
+attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
+                         const bf16* __restrict__ v_pages, const float* __restrict__ head_mix,
+                         const int* __restrict__ work, const int* __restrict__ q_start,
+                         const int* __restrict__ context_len, const int* __restrict__ block_table, int table_width,
+                         int page_size, int n_q, int n_kv, int head_dim, int v_dim, float scale, int window,
+                         int keep_first, float out_scale, int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    const MmaSmem L(n_q, n_kv, head_dim, v_dim);
+    bf16* qs = reinterpret_cast<bf16*>(raw + L.qs);
+    bf16* kv = reinterpret_cast<bf16*>(raw + L.kv);
+    bf16* phi = reinterpret_cast<bf16*>(raw + L.phi);
+    bf16* plo = reinterpret_cast<bf16*>(raw + L.plo);
+    float* sraw = reinterpret_cast<float*>(raw + L.sraw);
+    float* mix = reinterpret_cast<float*>(raw + L.mix);
+    float* m_run = reinterpret_cast<float*>(raw + L.m_run);
+    float* l_run = reinterpret_cast<float*>(raw + L.l_run);
+    float* corr = reinterpret_cast<float*>(raw + L.corr);
+    int* pg = reinterpret_cast<int*>(raw + L.pg);
+    int* sl = pg + KT;
+    const int ldq = L.ldq, ldkv = L.ldkv, lds = L.lds, ldp = L.ldp;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, tig = lane & 3;                      // fragment coordinates
+    const int e = work[2 * blockIdx.x], t0 = work[2 * blockIdx.x + 1];
+    const int row0 = q_start[e] + t0;
+    const int n_tok = min(QB, q_start[e + 1] - row0);
+    const int pos0 = context_len[e] + t0;                           // position of the block's first query
+    const int pos_hi = pos0 + n_tok - 1;
+    const int* table = block_table + (size_t)e * table_width;
+    const int group = n_q / n_kv;
+
+    // the block's queries (zero rows beyond the entry's end), the mix, the running softmax state
+    const int qchunks = head_dim / 8;
+    for (int i = tid; i < n_q * QB * qchunks; i += MMA_THREADS) {
+        const int c = i % qchunks, r = (i / qchunks) % QB, h = i / (qchunks * QB);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_tok) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + r) * n_q + h) * head_dim + c * 8);
+        *reinterpret_cast<uint4*>(qs + ((size_t)h * QB + r) * ldq + c * 8) = v;
+    }
+    if (head_mix != nullptr)
+        for (int i = tid; i < n_q * n_q; i += MMA_THREADS) mix[i] = head_mix[i];
+    for (int i = tid; i < n_q * QB; i += MMA_THREADS) { m_run[i] = -INFINITY; l_run[i] = 0.f; corr[i] = 1.f; }
+    float o[HPW][VB][4];
+#pragma unroll
+    for (int a = 0; a < HPW; ++a)
+#pragma unroll
+        for (int b = 0; b < VB; ++b) o[a][b][0] = o[a][b][1] = o[a][b][2] = o[a][b][3] = 0.f;
+
+    // key tiles any query of the block sees: the kept tokens that lie before the window's first
+    // tile, then the window's tiles (a kept token inside those is met there)
+    const int first_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+    const int kept_hi = window > 0 ? min(keep_first, pos_hi + 1) : 0;
+    const int win0 = first_lo / KT;
+    const int kept_only = min((kept_hi + KT - 1) / KT, win0);
+    const int n_tiles = kept_only + pos_hi / KT - win0 + 1;
+    const int kchunks = head_dim / 8, vchunks = v_dim / 8;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int j0 = it < kept_only ? it * KT : (win0 + it - kept_only) * KT;
+        __syncthreads();                                            // the tile before is done with kv and P
+        if (tid < KT) {
+            const int j = j0 + tid;
+            int page = -1;
+            if (j <= pos_hi && (j >= first_lo || j < kept_hi)) {    // a key some query of the block may see
+                page = j / page_size < table_width ? table[j / page_size] : -1;
+                if (page < 0) atomicExch(status, 3);
+            }
+            pg[tid] = page;
+            sl[tid] = j % page_size;
+        }
+        __syncthreads();
+        for (int i = tid; i < n_kv * KT * kchunks; i += MMA_THREADS) {
+            const int c = i % kchunks, jj = (i / kchunks) % KT, g = i / (kchunks * KT);
+            const bool ok = pg[jj] >= 0;
+            const bf16* src = ok ? k_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * head_dim + c * 8 : k_pages;
+            cp_async16(smem_address(kv + ((size_t)g * KT + jj) * ldkv + c * 8), src, ok ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+        // ---- S^T = K Q^T for the heads this warp owns
+#pragma unroll
+        for (int hh = 0; hh < HPW; ++hh) {
+            const int h = warp + 8 * hh;
+            if (h >= n_q) break;
+            const bf16* kg = kv + (size_t)(h / group) * KT * ldkv;
+            const bf16* qh = qs + (size_t)h * QB * ldq;
+            float c[2][4];
+#pragma unroll
+            for (int mb = 0; mb < 2; ++mb) c[mb][0] = c[mb][1] = c[mb][2] = c[mb][3] = 0.f;
+            for (int k0 = 0; k0 < head_dim; k0 += 16) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(qh + (size_t)gid * ldq + k0 + tig * 2);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(qh + (size_t)gid * ldq + k0 + 8 + tig * 2);
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb) {
+                    const bf16* kr = kg + (size_t)(mb * 16 + gid) * ldkv + k0 + tig * 2;
+                    uint32_t a[4];
+                    a[0] = *reinterpret_cast<const uint32_t*>(kr);
+                    a[1] = *reinterpret_cast<const uint32_t*>(kr + 8 * ldkv);
+                    a[2] = *reinterpret_cast<const uint32_t*>(kr + 8);
+                    a[3] = *reinterpret_cast<const uint32_t*>(kr + 8 * ldkv + 8);
+                    mma_16816(c[mb], a, b0, b1);
+                }
+            }
+            float* sh = sraw + (size_t)h * QB * lds;
+#pragma unroll
+            for (int mb = 0; mb < 2; ++mb) {
+                const int key = mb * 16 + gid;
+                sh[(tig * 2) * lds + key] = c[mb][0] * scale;
+                sh[(tig * 2 + 1) * lds + key] = c[mb][1] * scale;
+                sh[(tig * 2) * lds + key + 8] = c[mb][2] * scale;
+                sh[(tig * 2 + 1) * lds + key + 8] = c[mb][3] * scale;
+            }
+        }
+        __syncthreads();                                            // all scores are there; K is no longer needed
+        for (int i = tid; i < n_kv * KT * vchunks; i += MMA_THREADS) {
+            const int c = i % vchunks, jj = (i / vchunks) % KT, g = i / (vchunks * KT);
+            const bool ok = pg[jj] >= 0;
+            const bf16* src = ok ? v_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * v_dim + c * 8 : v_pages;
+            cp_async16(smem_address(kv + ((size_t)g * KT + jj) * ldkv + c * 8), src, ok ? 16 : 0);
+        }
+        cp_async_commit();
+        // ---- mix, mask, softmax step: a warp per (head, query) row, lane = key
+        for (int row = warp; row < n_q * QB; row += MMA_THREADS / 32) {
+            const int h = row / QB, r = row % QB;
+            float s;
+            if (head_mix != nullptr) {
+                s = 0.f;
+                for (int g = 0; g < n_q; ++g) s = fmaf(mix[h * n_q + g], sraw[((size_t)g * QB + r) * lds + lane], s);
+            } else {
+                s = sraw[(size_t)row * lds + lane];
+            }
+            const int pos = pos0 + r, j = j0 + lane;
+            const bool vis = r < n_tok && pg[lane] >= 0 && j <= pos && (window == 0 || pos - j < window || j < keep_first) &&
+                             (it >= kept_only || j < first_lo);      // a kept tile ends where the window's tiles begin
+            if (!vis) s = -INFINITY;
+            const float m_old = m_run[row];
+            const float m_new = fmaxf(m_old, warp_max(s));
+            float p = 0.f, c = 1.f;
+            if (m_new != -INFINITY) {
+                p = s == -INFINITY ? 0.f : expf(s - m_new);
+                c = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+            }
+            const float psum = warp_sum(p);
+            const bf16 hi = __float2bfloat16_rn(p);
+            phi[(size_t)row * ldp + lane] = hi;
+            plo[(size_t)row * ldp + lane] = __float2bfloat16_rn(p - __bfloat162float(hi));
+            __syncwarp();
+            if (lane == 0) {
+                l_run[row] = l_run[row] * c + psum;
+                m_run[row] = m_new;
+                corr[row] = c;
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();                                            // V has landed, the weights are written
+        // ---- O^T += V^T P^T for the heads this warp owns
+#pragma unroll
+        for (int hh = 0; hh < HPW; ++hh) {
+            const int h = warp + 8 * hh;
+            if (h >= n_q) break;
+            const bf16* vg = kv + (size_t)(h / group) * KT * ldkv;
+            const float c0 = corr[h * QB + tig * 2], c1 = corr[h * QB + tig * 2 + 1];
+            uint32_t bh[2][2], bl[2][2];
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+                const size_t at = ((size_t)h * QB + gid) * ldp + ks * 16 + tig * 2;
+                bh[ks][0] = *reinterpret_cast<const uint32_t*>(phi + at);
+                bh[ks][1] = *reinterpret_cast<const uint32_t*>(phi + at + 8);
+                bl[ks][0] = *reinterpret_cast<const uint32_t*>(plo + at);
+                bl[ks][1] = *reinterpret_cast<const uint32_t*>(plo + at + 8);
+            }
+#pragma unroll
+            for (int vb = 0; vb < VB; ++vb) {
+                if (vb * 16 >= v_dim) break;
+                float* acc = o[hh][vb];
+                acc[0] *= c0; acc[1] *= c1; acc[2] *= c0; acc[3] *= c1;
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) {
+                    const unsigned short* v0 = reinterpret_cast<const unsigned short*>(vg) + (size_t)(ks * 16 + tig * 2) * ldkv + vb * 16 + gid;
+                    uint32_t a[4];
+                    a[0] = (uint32_t)v0[0] | ((uint32_t)v0[ldkv] << 16);
+                    a[1] = (uint32_t)v0[8] | ((uint32_t)v0[ldkv + 8] << 16);
+                    a[2] = (uint32_t)v0[8 * ldkv] | ((uint32_t)v0[9 * ldkv] << 16);
+                    a[3] = (uint32_t)v0[8 * ldkv + 8] | ((uint32_t)v0[9 * ldkv + 8] << 16);
+                    mma_16816(acc, a, bh[ks][0], bh[ks][1]);
+                    mma_16816(acc, a, bl[ks][0], bl[ks][1]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < HPW; ++hh) {
+        const int h = warp + 8 * hh;
+        if (h >= n_q) break;
+        const float l0 = l_run[h * QB + tig * 2], l1 = l_run[h * QB + tig * 2 + 1];
+        const float i0 = l0 > 0.f ? out_scale / l0 : 0.f, i1 = l1 > 0.f ? out_scale / l1 : 0.f;
+#pragma unroll
+        for (int vb = 0; vb < VB; ++vb) {
+            if (vb * 16 >= v_dim) break;
+            const int vd = vb * 16 + gid;
+            if (tig * 2 < n_tok) {
+                bf16* dst = out + ((size_t)(row0 + tig * 2) * n_q + h) * v_dim;
+                dst[vd] = __float2bfloat16_rn(o[hh][vb][0] * i0);
+                dst[vd + 8] = __float2bfloat16_rn(o[hh][vb][2] * i0);
+            }
+            if (tig * 2 + 1 < n_tok) {
+                bf16* dst = out + ((size_t)(row0 + tig * 2 + 1) * n_q + h) * v_dim;
+                dst[vd] = __float2bfloat16_rn(o[hh][vb][1] * i1);
+                dst[vd + 8] = __float2bfloat16_rn(o[hh][vb][3] * i1);
+            }
+        }
+    }
+}
+
+template <int HPW, int VB, typename... Args>
+int launch_mix_mma(size_t smem, int items, cudaStream_t s, Args... args) {
+    auto kernel = attention_mix_mma_kernel<HPW, VB>;
+    static size_t allowed = 0;
+    if (smem > 48 * 1024 && smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+        allowed = smem;
+    }
+    return kipp_launch(kernel, dim3((unsigned)items), dim3(MMA_THREADS), smem, s, 1, args...);
+}
 }  // namespace
+
+// Whether the tensor-core prompt kernel takes these sizes (bfloat16 only).
+extern "C" int kipp_attention_mix_mma_ok(int n_q, int n_kv, int head_dim, int v_dim) {
+    if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q > 32) return 0;
+    if (head_dim <= 0 || v_dim <= 0 || head_dim % 16 || v_dim % 16 || v_dim > 128) return 0;
+    return MmaSmem(n_q, n_kv, head_dim, v_dim).bytes <= 220 * 1024 ? 1 : 0;
+}
+extern "C" int kipp_attention_mix_mma_tile() { return QB; }
+
+// work: (entry, first token) per block of 8 tokens, over every entry of the step.
+extern "C" int kipp_attention_mix_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
+                                      const float* head_mix, const int* work, int n_items, const int* q_start,
+                                      const int* context_len, const int* block_table, int table_width,
+                                      int page_size, int n_q, int n_kv, int head_dim, int v_dim, float scale,
+                                      int window, int keep_first, float out_scale, int* status, void* stream) {
+    if (n_items <= 0) return 0;
+    if (!kipp_attention_mix_mma_ok(n_q, n_kv, head_dim, v_dim) || page_size <= 0 || window < 0 || keep_first < 0)
+        return KIPP_ERR_ARG;
+    if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) != 0) return -3;
+    const size_t smem = MmaSmem(n_q, n_kv, head_dim, v_dim).bytes;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int hpw = (n_q + 7) / 8, vb = (v_dim + 15) / 16;
+#define KIPP_MIX_MMA(H, V)                                                                                             \
+    return launch_mix_mma<H, V>(smem, n_items, s, (bf16*)out, (const bf16*)q, (const bf16*)k_pages,                    \
+                                (const bf16*)v_pages, head_mix, work, q_start, context_len, block_table, table_width,  \
+                                page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, status)
+    if (hpw <= 1) { if (vb <= 2) KIPP_MIX_MMA(1, 2); if (vb <= 4) KIPP_MIX_MMA(1, 4); KIPP_MIX_MMA(1, 8); }
+    if (hpw <= 2) { if (vb <= 2) KIPP_MIX_MMA(2, 2); if (vb <= 4) KIPP_MIX_MMA(2, 4); KIPP_MIX_MMA(2, 8); }
+    if (vb <= 2) KIPP_MIX_MMA(4, 2);
+    if (vb <= 4) KIPP_MIX_MMA(4, 4);
+    KIPP_MIX_MMA(4, 8);
+#undef KIPP_MIX_MMA
+}
 
 // Runs a step of `tokens` tokens is cut into (1: every token walks its keys in one block): few
 // tokens with many keys are cut so that the GPU has blocks to run.  max_keys bounds the context.

@@ -337,9 +337,18 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
         const int write = (run.writes_cache ? 1 : 0) | (ctx.kv_round_bf16 && ctx.dtype == F32 ? 2 : 0);
         ops.qk_norm_rope_write(qkv, qkv_cols, q, cache, ctx.dtype, qn, kn, norm_dtype_, eps_, cos_sin, rot, m.positions,
                                m.entry_of_token, T, heads_, kv_heads_, head_dim_, write, v_dim_);
+        const int* tiles = nullptr;
+        int n_tiles = 0;
+        if (mix_planner_) {
+            auto it = m.work.find(mix_planner_->key());
+            if (it != m.work.end()) {
+                tiles = it->second[0];
+                n_tiles = m.work_sizes.at(mix_planner_->key())[0] / 2;
+            }
+        }
         ops.attention_mix(attn, q, cache, ctx.dtype, head_mix_, m.positions, m.entry_of_token, T, heads_, kv_heads_,
                           head_dim_, v_dim_, scale_, window_, window_ > 0 ? opt_.keep_first : 0,
-                          (float)opt_.output_scale);
+                          (float)opt_.output_scale, tiles, n_tiles, m.q_start, m.context_len);
         const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
         ops.gemm(residual, F32, hidden_, attn, o_dim_, w_o_, o_dim_, dtype_, T, hidden_, o_dim_, EPI_ADD, emit);
         fold_emitted(ctx, emit, hidden_);
@@ -1425,6 +1434,7 @@ inline std::string Engine::info_json() {
     counters.set("folded_norms", ops_.folded_norms);
     counters.set("stream_decode_launches", ops_.stream_decode_launches);
     counters.set("projections_to_heads", ops_.projections_to_heads);
+    counters.set("mix_mma_launches", ops_.mix_mma_launches);
     j.set("counters", std::move(counters));
     info_ = j.dump();
     return info_;

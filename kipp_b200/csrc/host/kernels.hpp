@@ -82,6 +82,7 @@ public:
     Workspace* workspace = nullptr;
     long long launches = 0;                // kernels of this package launched through this object
     bool prefill_tensor_core = true;       // prompt portions on tcgen05 where the sizes allow
+    bool mix_tensor_core = true;           // prompt steps of the mixed-head attention on mma.sync where the sizes allow
 
     static constexpr int DECODE_MAX_SPLITS = 32;
     static constexpr int PREFILL_TC_MIN_TOKENS = 64;   // shorter portions waste a 128-row tile
@@ -216,16 +217,43 @@ public:
     // Attention whose heads' scores are mixed before the softmax (head_mix [n_q, n_q] float32, or
     // null), with a window that keeps the first keep_first positions and value heads of v_dim;
     // the result is scaled by out_scale.  Scores, mix, softmax and weighted sum in float32.
+    // Tokens per work item of the tensor-core prompt kernel of attention_mix.
+    static int attention_mix_tile() {
+        using Fn = int (*)();
+        static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix_mma_tile");
+        return f();
+    }
+    // Steps of more than this many tokens take the tensor-core kernel where it takes the sizes;
+    // shorter ones are cut into runs of keys on the CUDA-core kernel.
+    static constexpr int MIX_MMA_MIN_TOKENS = 64;
+    // `tiles`: (entry, first token) per attention_mix_tile() tokens over every entry of the step
+    // (MixTilePlanner), or null.
     void attention_mix(void* out, const void* q, const PagedCacheView& cache, int dtype, const float* head_mix,
                        const int* positions, const int* entry_of_token, int tokens, int n_q, int n_kv, int head_dim,
-                       int v_dim, float scale, int window, int keep_first, float out_scale) {
+                       int v_dim, float scale, int window, int keep_first, float out_scale, const int* tiles = nullptr,
+                       int n_tiles = 0, const int* q_start = nullptr, const int* context_len = nullptr) {
         using Fn = int (*)(void*, const void*, const void*, const void*, int, const float*, const int*, const int*,
                            const int*, int, int, int, int, int, int, int, float, int, int, float, int, float*, int*, void*);
         using Fr = int (*)(int, int, int, int);
         using Fs = long long (*)(int, int, int, int);
+        using Fo = int (*)(int, int, int, int);
+        using Fm = int (*)(void*, const void*, const void*, const void*, const float*, const int*, int, const int*,
+                           const int*, const int*, int, int, int, int, int, int, float, int, int, float, int*, void*);
         static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix");
         static Fr runs_of = kernel_symbol<Fr>("attention_mix", "kipp_attention_mix_runs");
         static Fs scratch_of = kernel_symbol<Fs>("attention_mix", "kipp_attention_mix_scratch_floats");
+        static Fo mma_ok = kernel_symbol<Fo>("attention_mix", "kipp_attention_mix_mma_ok");
+        static Fm mma = kernel_symbol<Fm>("attention_mix", "kipp_attention_mix_mma");
+        const bool aligned = (((uintptr_t)out | (uintptr_t)q | (uintptr_t)cache.k_pages | (uintptr_t)cache.v_pages) & 15) == 0;
+        if (dtype == BF16 && mix_tensor_core && tokens > MIX_MMA_MIN_TOKENS && tiles != nullptr && n_tiles > 0 && aligned &&
+            mma_ok(n_q, n_kv, head_dim, v_dim)) {
+            run(mma(out, q, cache.k_pages, cache.v_pages, head_mix, tiles, n_tiles, q_start, context_len, cache.block_table,
+                    cache.table_width, cache.page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale,
+                    status, stream),
+                "attention_mix_mma");
+            ++mix_mma_launches;
+            return;
+        }
         // a step of few tokens is cut into runs of keys (the table's width bounds the context)
         const int runs = runs_of(tokens, window, keep_first, cache.table_width * cache.page_size);
         float* partial = runs > 1 ? workspace->get<float>("attention_mix_runs", (size_t)scratch_of(tokens, runs, n_q, v_dim))
@@ -521,6 +549,7 @@ public:
     long long folded_norms = 0;          // norms that ran inside the products around them
     long long stream_decode_launches = 0;   // decode attention dealt out as a stream
     long long projections_to_heads = 0;     // q/k/v projections with norm, rotation and cache write inside
+    long long mix_mma_launches = 0;         // launches of the tensor-core kernel of the mixed-head attention
 };
 
 }  // namespace kipp

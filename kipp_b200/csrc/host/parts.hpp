@@ -290,6 +290,29 @@ private:
     bool own_length_;
 };
 
+// The work list of the mixed-head attention's tensor-core prompt kernel: (entry, first token)
+// per tile of `tile` tokens over every entry of the step.
+class MixTilePlanner : public WorkPlanner {
+public:
+    explicit MixTilePlanner(int tile) : tile_(std::max(tile, 1)) {}
+    static std::string key_for(int tile) { return format("attention_mix/tiles%d", tile); }
+    std::string key() const override { return key_for(tile_); }
+    int sections() const override { return 1; }
+    void sizes(const StepShape& s, int* n) const override {
+        int items = 0;
+        for (int q : s.q_lens) items += (q + tile_ - 1) / tile_;
+        n[0] = 2 * items;
+    }
+    void fill(const StepShape& s, int* const* sec) const override {
+        int a = 0;
+        for (int i = 0; i < s.entries; ++i)
+            for (int t = 0; t < s.q_lens[(size_t)i]; t += tile_) { sec[0][a++] = i; sec[0][a++] = t; }
+    }
+
+private:
+    int tile_;
+};
+
 // ---------------------------------------------------------------------------------------------
 // Norms in deferred form (see NormFold, StepContext::input_scale): what a part's first product and
 // its residual add pass to the kernels, and what a block runs where no residual add left the form.
@@ -423,7 +446,10 @@ public:
         return PagedKVSpec{kv_heads_, head_dim_, window_, v_dim_, window_ > 0 ? opt_.keep_first : 0};
     }
     std::shared_ptr<WorkPlanner> planner(const DeviceInfo& dev, bool own_length) override {
-        if (mix_path_) return nullptr;            // the attention_mix kernel reads the common metadata only
+        if (mix_path_) {                          // (entry, first token) per tile of its tensor-core prompt kernel
+            mix_planner_ = std::make_shared<MixTilePlanner>(Ops::attention_mix_tile());
+            return mix_planner_;
+        }
         auto p = std::make_shared<AttentionPlanner>(kv_heads_, dev.sm_count, own_length);
         planner_ = p;
         return p;
@@ -481,6 +507,7 @@ private:
     void *w_qkv_ = nullptr, *w_o_ = nullptr, *q_norm_ = nullptr, *k_norm_ = nullptr;
     float* head_mix_ = nullptr;
     std::shared_ptr<AttentionPlanner> planner_;
+    std::shared_ptr<MixTilePlanner> mix_planner_;
 };
 
 // Dense SwiGLU feed-forward: x += W_down (silu(W_gate n) * (W_up n)) (src/kipp.c:2994-3010,

@@ -60,9 +60,15 @@ CONFIGS = {
                                     retention(1, 128, 128, [0.99], 64), 192),
                      delta_layer(1, 128, 16, 128)],
           "loop": {"start": 2, "stop": 4, "times": 2}},
+    # sizes that fit no vector width: an odd vocabulary, a width that is no multiple of 8, head
+    # sizes of 6, 5, 10 and 3, three heads on one key/value head
+    "S": {"architecture": "Venizen", "vocab": 101, "width": 100, "norm": {"eps": 2e-5},
+          "layers": [parallel_layer(attention(3, 1, 6, 5, 9, 2, 2, scale=0.7), retention(1, 10, 3, [0.8], 6), 50),
+                     delta_layer(2, 6, 3, None)],
+          "loop": {"start": 0, "stop": 2, "times": 2}},
 }
 INIT = {"P": dict(seed=3, sigma=0.15, norm_jitter=0.2), "Q": dict(seed=5, sigma=0.12, norm_jitter=0.1),
-        "R": dict(seed=9, sigma=0.08, norm_jitter=0.15)}
+        "R": dict(seed=9, sigma=0.08, norm_jitter=0.15), "S": dict(seed=12, sigma=0.2, norm_jitter=0.1)}
 
 _tmp = tempfile.TemporaryDirectory(prefix="kipp_b200_venizen_")
 
