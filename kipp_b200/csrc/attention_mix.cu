@@ -454,36 +454,71 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
             cp_async16(smem_address(kv + ((size_t)g * KT + jj) * ldkv + c * 8), src, ok ? 16 : 0);
         }
         cp_async_commit();
-        // ---- mix, mask, softmax step: a warp per (head, query) row, lane = key
-        for (int row = warp; row < n_q * QB; row += MMA_THREADS / 32) {
-            const int h = row / QB, r = row % QB;
-            float s;
+        // ---- mix, mask, softmax step: a warp per (head, query) row, lane = key; four rows at a
+        // time, so that their chains of dependent shuffles and multiply-adds overlap
+        constexpr int RI = 4;
+        const int n_rows = n_q * QB;
+        for (int base = warp; base < n_rows; base += RI * (MMA_THREADS / 32)) {
+            float sv[RI], m_old[RI], mx[RI], p[RI], c[RI], ps[RI];
+            int rows[RI];
+#pragma unroll
+            for (int i = 0; i < RI; ++i) {
+                rows[i] = min(base + i * (MMA_THREADS / 32), n_rows - 1);       // a row beyond the end repeats the last one (not stored)
+                sv[i] = 0.f;
+            }
             if (head_mix != nullptr) {
-                s = 0.f;
-                for (int g = 0; g < n_q; ++g) s = fmaf(mix[h * n_q + g], sraw[((size_t)g * QB + r) * lds + lane], s);
+                for (int g = 0; g < n_q; ++g) {
+#pragma unroll
+                    for (int i = 0; i < RI; ++i)
+                        sv[i] = fmaf(mix[(rows[i] / QB) * n_q + g], sraw[((size_t)g * QB + rows[i] % QB) * lds + lane], sv[i]);
+                }
             } else {
-                s = sraw[(size_t)row * lds + lane];
+#pragma unroll
+                for (int i = 0; i < RI; ++i) sv[i] = sraw[(size_t)rows[i] * lds + lane];
             }
-            const int pos = pos0 + r, j = j0 + lane;
-            const bool vis = r < n_tok && pg[lane] >= 0 && j <= pos && (window == 0 || pos - j < window || j < keep_first) &&
-                             (it >= kept_only || j < first_lo);      // a kept tile ends where the window's tiles begin
-            if (!vis) s = -INFINITY;
-            const float m_old = m_run[row];
-            const float m_new = fmaxf(m_old, warp_max(s));
-            float p = 0.f, c = 1.f;
-            if (m_new != -INFINITY) {
-                p = s == -INFINITY ? 0.f : expf(s - m_new);
-                c = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+            const int j = j0 + lane;
+#pragma unroll
+            for (int i = 0; i < RI; ++i) {
+                const int r = rows[i] % QB, pos = pos0 + r;
+                const bool vis = r < n_tok && pg[lane] >= 0 && j <= pos && (window == 0 || pos - j < window || j < keep_first);
+                if (!vis) sv[i] = -INFINITY;
+                m_old[i] = m_run[rows[i]];
+                mx[i] = sv[i];
             }
-            const float psum = warp_sum(p);
-            const bf16 hi = __float2bfloat16_rn(p);
-            phi[(size_t)row * ldp + lane] = hi;
-            plo[(size_t)row * ldp + lane] = __float2bfloat16_rn(p - __bfloat162float(hi));
+#pragma unroll
+            for (int x = 16; x > 0; x >>= 1) {
+#pragma unroll
+                for (int i = 0; i < RI; ++i) mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], x));
+            }
+#pragma unroll
+            for (int i = 0; i < RI; ++i) {
+                mx[i] = fmaxf(mx[i], m_old[i]);
+                p[i] = 0.f;
+                c[i] = 1.f;
+                if (mx[i] != -INFINITY) {
+                    p[i] = sv[i] == -INFINITY ? 0.f : expf(sv[i] - mx[i]);
+                    c[i] = m_old[i] == -INFINITY ? 0.f : expf(m_old[i] - mx[i]);
+                }
+                ps[i] = p[i];
+            }
+#pragma unroll
+            for (int x = 16; x > 0; x >>= 1) {
+#pragma unroll
+                for (int i = 0; i < RI; ++i) ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], x);
+            }
             __syncwarp();
-            if (lane == 0) {
-                l_run[row] = l_run[row] * c + psum;
-                m_run[row] = m_new;
-                corr[row] = c;
+#pragma unroll
+            for (int i = 0; i < RI; ++i) {
+                if (base + i * (MMA_THREADS / 32) >= n_rows) continue;
+                const int row = rows[i];
+                const bf16 hi = __float2bfloat16_rn(p[i]);
+                phi[(size_t)row * ldp + lane] = hi;
+                plo[(size_t)row * ldp + lane] = __float2bfloat16_rn(p[i] - __bfloat162float(hi));
+                if (lane == 0) {
+                    l_run[row] = l_run[row] * c[i] + ps[i];
+                    m_run[row] = mx[i];
+                    corr[row] = c[i];
+                }
             }
         }
         cp_async_wait<0>();

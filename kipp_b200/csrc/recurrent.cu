@@ -149,8 +149,9 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     constexpr int NV = DELTA ? 5 : 2;
     const int D = a.dim, V = a.v_dim, TB = a.batch;
     const int nvd = NV * D, rec = nvd + V;
-    float* tv[2] = {smem, smem + (size_t)TB * (nvd + VS)};      // [TB][NV][D] twice
-    float* vv[2] = {tv[0] + (size_t)TB * nvd, tv[1] + (size_t)TB * nvd};   // [TB][VS] twice
+    // two buffers of [TB][NV][D] vectors followed by [TB][VS] values; their addresses are formed
+    // from the shared base each time (a table of pointers would turn the loads into generic ones)
+    const int buf_floats = TB * (nvd + VS);
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x;
@@ -170,19 +171,19 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     for (int i = 0; i < CHUNK; ++i) S[i] = (live && d0 + i < D) ? S_slot[(size_t)(d0 + i) * V + col] : 0.f;
     const float decay = DELTA ? 0.f : a.decay[h];
 
-    load_batch<DELTA>(tv[0], vv[0], recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
+    load_batch<DELTA>(smem, smem + TB * nvd, recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
     int buf = 0;
     for (int t0 = 0; t0 < n_tok; t0 += TB, buf ^= 1) {
         const int nb = min(TB, n_tok - t0);
         if (t0 + TB < n_tok)
-            load_batch<DELTA>(tv[buf ^ 1], vv[buf ^ 1], recs + (size_t)(t0 + TB) * rec, rec, nvd, min(TB, n_tok - t0 - TB),
-                              slice, V, async, VS * P);
+            load_batch<DELTA>(smem + (buf ^ 1) * buf_floats, smem + (buf ^ 1) * buf_floats + TB * nvd,
+                              recs + (size_t)(t0 + TB) * rec, rec, nvd, min(TB, n_tok - t0 - TB), slice, V, async, VS * P);
         else
             cp_async_commit();
         cp_async_wait<1>();                 // this batch has landed; the next one may still be on its way
         __syncthreads();
-        const float* tvb = tv[buf];
-        const float* vvb = vv[buf];
+        const float* tvb = smem + buf * buf_floats;
+        const float* vvb = tvb + TB * nvd;
         for (int tt = 0; tt < nb; ++tt) {
             const float v = vvb[tt * VS + cl];
             const float* base = tvb + tt * nvd + d0;
