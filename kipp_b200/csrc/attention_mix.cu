@@ -72,7 +72,7 @@ __device__ __forceinline__ void visible_runs(int pos, int window, int keep_first
     kept = min(keep_first, first);
 }
 
-constexpr int SPLIT_TILES = 4;     // key tiles per run when a step's tokens are cut into runs
+constexpr int SPLIT_TILES = 2;     // key tiles per run when a step's tokens are cut into runs
 
 // Rows of `elems` elements from the pages into shared memory (row stride ld), 16 bytes at a time
 // where the sizes allow; rows of keys that are not visible become zeros.
@@ -372,8 +372,8 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         if (r < n_tok) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + r) * n_q + h) * head_dim + c * 8);
         *reinterpret_cast<uint4*>(qs + ((size_t)h * QB + r) * ldq + c * 8) = v;
     }
-    if (head_mix != nullptr)
-        for (int i = tid; i < n_q * n_q; i += MMA_THREADS) mix[i] = head_mix[i];
+    if (head_mix != nullptr)                                        // transposed: mix[g][h], the heads a lane mixes side by side
+        for (int i = tid; i < n_q * n_q; i += MMA_THREADS) mix[(i % n_q) * n_q + i / n_q] = head_mix[i];
     for (int i = tid; i < n_q * QB; i += MMA_THREADS) { m_run[i] = -INFINITY; l_run[i] = 0.f; corr[i] = 1.f; }
     float o[HPW][VB][4];
 #pragma unroll
@@ -403,11 +403,13 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
             sl[tid] = j % page_size;
         }
         __syncthreads();
-        for (int i = tid; i < n_kv * KT * kchunks; i += MMA_THREADS) {
-            const int c = i % kchunks, jj = (i / kchunks) % KT, g = i / (kchunks * KT);
+        // eight threads per row of the tile (row = kv head x key), each every eighth 16-byte chunk
+        for (int rr = tid >> 3; rr < n_kv * KT; rr += MMA_THREADS / 8) {
+            const int jj = rr & (KT - 1), g = rr / KT;
             const bool ok = pg[jj] >= 0;
-            const bf16* src = ok ? k_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * head_dim + c * 8 : k_pages;
-            cp_async16(smem_address(kv + ((size_t)g * KT + jj) * ldkv + c * 8), src, ok ? 16 : 0);
+            const bf16* src = ok ? k_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * head_dim : k_pages;
+            const uint32_t dst = smem_address(kv + (size_t)rr * ldkv);
+            for (int c = tid & 7; c < kchunks; c += 8) cp_async16(dst + c * 16, ok ? src + c * 8 : src, ok ? 16 : 0);
         }
         cp_async_commit();
         cp_async_wait<0>();
@@ -447,40 +449,47 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
             }
         }
         __syncthreads();                                            // all scores are there; K is no longer needed
-        for (int i = tid; i < n_kv * KT * vchunks; i += MMA_THREADS) {
-            const int c = i % vchunks, jj = (i / vchunks) % KT, g = i / (vchunks * KT);
+        for (int rr = tid >> 3; rr < n_kv * KT; rr += MMA_THREADS / 8) {
+            const int jj = rr & (KT - 1), g = rr / KT;
             const bool ok = pg[jj] >= 0;
-            const bf16* src = ok ? v_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * v_dim + c * 8 : v_pages;
-            cp_async16(smem_address(kv + ((size_t)g * KT + jj) * ldkv + c * 8), src, ok ? 16 : 0);
+            const bf16* src = ok ? v_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * v_dim : v_pages;
+            const uint32_t dst = smem_address(kv + (size_t)rr * ldkv);
+            for (int c = tid & 7; c < vchunks; c += 8) cp_async16(dst + c * 16, ok ? src + c * 8 : src, ok ? 16 : 0);
         }
         cp_async_commit();
-        // ---- mix, mask, softmax step: a warp per (head, query) row, lane = key; four rows at a
-        // time, so that their chains of dependent shuffles and multiply-adds overlap
+        // ---- mix, mask, softmax step: warp = query, lane = key, four heads at a time: the four
+        // rows share each score they mix, and their chains of dependent shuffles overlap
         constexpr int RI = 4;
-        const int n_rows = n_q * QB;
-        for (int base = warp; base < n_rows; base += RI * (MMA_THREADS / 32)) {
+        static_assert(MMA_THREADS / 32 == QB, "one warp per query of the block");
+        const int r = warp, pos = pos0 + r, j = j0 + lane;
+        const bool vis = r < n_tok && pg[lane] >= 0 && j <= pos && (window == 0 || pos - j < window || j < keep_first);
+        for (int h0 = 0; h0 < n_q; h0 += RI) {
             float sv[RI], m_old[RI], mx[RI], p[RI], c[RI], ps[RI];
             int rows[RI];
 #pragma unroll
             for (int i = 0; i < RI; ++i) {
-                rows[i] = min(base + i * (MMA_THREADS / 32), n_rows - 1);       // a row beyond the end repeats the last one (not stored)
+                rows[i] = min(h0 + i, n_q - 1) * QB + r;               // a head beyond the last repeats it (not stored)
                 sv[i] = 0.f;
             }
             if (head_mix != nullptr) {
+                const bool four = (n_q & 3) == 0;
                 for (int g = 0; g < n_q; ++g) {
+                    const float sg = sraw[((size_t)g * QB + r) * lds + lane];
+                    if (four) {
+                        const float4 m4 = *reinterpret_cast<const float4*>(mix + g * n_q + h0);
+                        sv[0] = fmaf(m4.x, sg, sv[0]); sv[1] = fmaf(m4.y, sg, sv[1]);
+                        sv[2] = fmaf(m4.z, sg, sv[2]); sv[3] = fmaf(m4.w, sg, sv[3]);
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < RI; ++i)
-                        sv[i] = fmaf(mix[(rows[i] / QB) * n_q + g], sraw[((size_t)g * QB + rows[i] % QB) * lds + lane], sv[i]);
+                        for (int i = 0; i < RI; ++i) sv[i] = fmaf(mix[g * n_q + min(h0 + i, n_q - 1)], sg, sv[i]);
+                    }
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < RI; ++i) sv[i] = sraw[(size_t)rows[i] * lds + lane];
             }
-            const int j = j0 + lane;
 #pragma unroll
             for (int i = 0; i < RI; ++i) {
-                const int r = rows[i] % QB, pos = pos0 + r;
-                const bool vis = r < n_tok && pg[lane] >= 0 && j <= pos && (window == 0 || pos - j < window || j < keep_first);
                 if (!vis) sv[i] = -INFINITY;
                 m_old[i] = m_run[rows[i]];
                 mx[i] = sv[i];
@@ -509,7 +518,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
             __syncwarp();
 #pragma unroll
             for (int i = 0; i < RI; ++i) {
-                if (base + i * (MMA_THREADS / 32) >= n_rows) continue;
+                if (h0 + i >= n_q) continue;
                 const int row = rows[i];
                 const bf16 hi = __float2bfloat16_rn(p[i]);
                 phi[(size_t)row * ldp + lane] = hi;
