@@ -81,13 +81,15 @@ __device__ __forceinline__ void stage_rows(T* __restrict__ dst, int ld, const T*
                                            int n_kv, int page_size, const int* pg, const int* sl, bool vec) {
     constexpr int VEC = Vec<T>::N;
     if (vec) {
-        // asynchronous copies: every chunk of the tile is in flight at once (the caller waits)
+        // asynchronous copies: every chunk of the tile is in flight at once (the caller waits);
+        // eight threads per row (row = kv head x key), each every eighth 16-byte chunk
         const int chunks = elems / VEC;
-        for (int i = threadIdx.x; i < n_kv * KT * chunks; i += THREADS) {
-            const int c = i % chunks, jj = (i / chunks) % KT, g = i / (chunks * KT);
+        for (int rr = threadIdx.x >> 3; rr < n_kv * KT; rr += THREADS / 8) {
+            const int jj = rr & (KT - 1), g = rr / KT;
             const bool ok = pg[jj] >= 0;
-            const T* src = ok ? pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * elems + c * VEC : pages;
-            cp_async16(smem_address(dst + ((size_t)g * KT + jj) * ld + c * VEC), src, ok ? 16 : 0);
+            const T* src = ok ? pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * elems : pages;
+            const uint32_t to = smem_address(dst + (size_t)rr * ld);
+            for (int c = threadIdx.x & 7; c < chunks; c += 8) cp_async16(to + c * 16, ok ? src + c * VEC : src, ok ? 16 : 0);
         }
     } else {
         for (int i = threadIdx.x; i < n_kv * KT * elems; i += THREADS) {
