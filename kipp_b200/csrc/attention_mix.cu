@@ -78,23 +78,25 @@ constexpr int SPLIT_TILES = 2;     // key tiles per run when a step's tokens are
 // where the sizes allow; rows of keys that are not visible become zeros.
 template <typename T>
 __device__ __forceinline__ void stage_rows(T* __restrict__ dst, int ld, const T* __restrict__ pages, int elems,
-                                           int n_kv, int page_size, const int* pg, const int* sl, bool vec) {
+                                           int n_kv, int g0, int ng, int page_size, const int* pg, const int* sl,
+                                           bool vec) {
+    // kv heads g0 .. g0 + ng - 1; row (g - g0) * KT + key of dst
     constexpr int VEC = Vec<T>::N;
     if (vec) {
         // asynchronous copies: every chunk of the tile is in flight at once (the caller waits);
         // eight threads per row (row = kv head x key), each every eighth 16-byte chunk
         const int chunks = elems / VEC;
-        for (int rr = threadIdx.x >> 3; rr < n_kv * KT; rr += THREADS / 8) {
-            const int jj = rr & (KT - 1), g = rr / KT;
+        for (int rr = threadIdx.x >> 3; rr < ng * KT; rr += THREADS / 8) {
+            const int jj = rr & (KT - 1), g = g0 + rr / KT;
             const bool ok = pg[jj] >= 0;
             const T* src = ok ? pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * elems : pages;
             const uint32_t to = smem_address(dst + (size_t)rr * ld);
             for (int c = threadIdx.x & 7; c < chunks; c += 8) cp_async16(to + c * 16, ok ? src + c * VEC : src, ok ? 16 : 0);
         }
     } else {
-        for (int i = threadIdx.x; i < n_kv * KT * elems; i += THREADS) {
-            const int c = i % elems, jj = (i / elems) % KT, g = i / (elems * KT);
-            dst[((size_t)g * KT + jj) * ld + c] =
+        for (int i = threadIdx.x; i < ng * KT * elems; i += THREADS) {
+            const int c = i % elems, jj = (i / elems) % KT, g = g0 + i / (elems * KT);
+            dst[(size_t)(i / elems) * ld + c] =
                 pg[jj] >= 0 ? pages[(((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * elems + c] : from_f32<T>(0.f);
         }
     }
@@ -109,7 +111,9 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
                      const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                      const int* __restrict__ block_table, int table_width, int page_size, int n_q, int n_kv,
                      int head_dim, int v_dim, float scale, int window, int keep_first, float out_scale,
-                     int split, float* __restrict__ partial, int* __restrict__ status) {
+                     int split, float* __restrict__ partial, int kv_stage, int* __restrict__ status) {
+    // kv_stage: kv heads whose keys (then values) of a tile are in shared memory at a time; all of
+    // them where they fit, else the tile is walked in passes over groups of kv heads
     extern __shared__ __align__(16) float smem[];
     const int ldk = head_dim + row_pad<T>(), ldv = v_dim + row_pad<T>();
     float* qs = smem;                              // [n_q][head_dim]
@@ -124,8 +128,8 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
     int* sl = pg + KT;                             // [KT] slot in page
     const size_t head_floats = ((size_t)n_q * head_dim + (size_t)n_q * n_q + 2 * (size_t)n_q * KT + (size_t)n_q * v_dim +
                                 3 * (size_t)n_q + 2 * KT + 3) / 4 * 4;
-    T* ktile = reinterpret_cast<T*>(smem + head_floats);           // [n_kv][KT][ldk]
-    T* vtile = ktile + (size_t)n_kv * KT * ldk;                    // [n_kv][KT][ldv]
+    T* ktile = reinterpret_cast<T*>(smem + head_floats);           // [kv_stage][KT][ldk]
+    T* vtile = ktile + (size_t)kv_stage * KT * ldk;                // [kv_stage][KT][ldv]
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -167,14 +171,19 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
             sl[tid] = j % page_size;
         }
         __syncthreads();
-        stage_rows(ktile, ldk, k_pages, head_dim, n_kv, page_size, pg, sl, kvec);
-        stage_rows(vtile, ldv, v_pages, v_dim, n_kv, page_size, pg, sl, vvec);
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
-        for (int idx = tid; idx < n_q * KT; idx += THREADS) {
-            const int h = idx / KT, jj = idx % KT;
-            sraw[idx] = dot_row(qs + h * head_dim, ktile + ((size_t)(h / group) * KT + jj) * ldk, head_dim, kvec) * scale;
+        for (int g0 = 0; g0 < n_kv; g0 += kv_stage) {
+            const int ng = min(kv_stage, n_kv - g0);
+            if (g0 > 0) __syncthreads();                           // the pass before has read its keys
+            stage_rows(ktile, ldk, k_pages, head_dim, n_kv, g0, ng, page_size, pg, sl, kvec);
+            if (g0 + ng >= n_kv && kv_stage >= n_kv)               // one pass: the values can come at once
+                stage_rows(vtile, ldv, v_pages, v_dim, n_kv, 0, n_kv, page_size, pg, sl, vvec);
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            for (int idx = tid; idx < ng * group * KT; idx += THREADS) {
+                const int hl = idx / KT, jj = idx % KT, h = g0 * group + hl;
+                sraw[h * KT + jj] = dot_row(qs + h * head_dim, ktile + ((size_t)(hl / group) * KT + jj) * ldk, head_dim, kvec) * scale;
+            }
         }
         __syncthreads();
         for (int h = warp; h < n_q; h += THREADS / 32) {
@@ -204,17 +213,27 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
         }
         __syncthreads();
         // rows of keys that are not visible hold zeros and have weight zero: no branch
-        for (int e = tid; e < n_q * v_dim; e += THREADS) {
-            const int h = e / v_dim, d = e % v_dim;
-            const T* vcol = vtile + (size_t)(h / group) * KT * ldv + d;
-            const float* ph = pw + h * KT;
-            float a0 = acc[e] * corr[h], a1 = 0.f;
-#pragma unroll 8
-            for (int jj = 0; jj < KT; jj += 2) {
-                a0 = fmaf(ph[jj], to_f32(vcol[(size_t)jj * ldv]), a0);
-                a1 = fmaf(ph[jj + 1], to_f32(vcol[(size_t)(jj + 1) * ldv]), a1);
+        for (int g0 = 0; g0 < n_kv; g0 += kv_stage) {
+            const int ng = min(kv_stage, n_kv - g0);
+            if (kv_stage < n_kv) {                                  // several passes: this group's values now
+                __syncthreads();
+                stage_rows(vtile, ldv, v_pages, v_dim, n_kv, g0, ng, page_size, pg, sl, vvec);
+                cp_async_commit();
+                cp_async_wait<0>();
+                __syncthreads();
             }
-            acc[e] = a0 + a1;
+            for (int el = tid; el < ng * group * v_dim; el += THREADS) {
+                const int hl = el / v_dim, d = el % v_dim, h = g0 * group + hl, e = h * v_dim + d;
+                const T* vcol = vtile + (size_t)(hl / group) * KT * ldv + d;
+                const float* ph = pw + h * KT;
+                float a0 = acc[e] * corr[h], a1 = 0.f;
+#pragma unroll 8
+                for (int jj = 0; jj < KT; jj += 2) {
+                    a0 = fmaf(ph[jj], to_f32(vcol[(size_t)jj * ldv]), a0);
+                    a1 = fmaf(ph[jj + 1], to_f32(vcol[(size_t)(jj + 1) * ldv]), a1);
+                }
+                acc[e] = a0 + a1;
+            }
         }
     }
     __syncthreads();
@@ -269,8 +288,13 @@ int launch_mix(void* out, const void* q, const void* k_pages, const void* v_page
                float out_scale, int runs, float* partial, int* status, cudaStream_t s) {
     const size_t head_floats = ((size_t)n_q * head_dim + (size_t)n_q * n_q + 2 * (size_t)n_q * KT + (size_t)n_q * v_dim +
                                 3 * (size_t)n_q + 2 * KT + 3) / 4 * 4;
-    const size_t smem = head_floats * sizeof(float) +
-                        (size_t)n_kv * KT * ((size_t)head_dim + v_dim + 2 * row_pad<T>()) * sizeof(T);
+    // kv heads staged at a time: all of them within about 100 KB of shared memory, else as many as fit
+    const size_t per_kv = (size_t)KT * ((size_t)head_dim + v_dim + 2 * row_pad<T>()) * sizeof(T);
+    const size_t head_bytes = head_floats * sizeof(float), budget = 100 * 1024;
+    int kv_stage = n_kv;
+    if (head_bytes + per_kv * n_kv > budget)
+        kv_stage = (int)std::max<size_t>(1, std::min<size_t>((size_t)n_kv, budget > head_bytes ? (budget - head_bytes) / per_kv : 1));
+    const size_t smem = head_bytes + per_kv * kv_stage;
     if (smem > 200 * 1024) return KIPP_ERR_ARG;
     auto kernel = attention_mix_kernel<T>;
     static size_t allowed = 0;
@@ -283,7 +307,7 @@ int launch_mix(void* out, const void* q, const void* k_pages, const void* v_page
     int rc = kipp_launch(kernel, dim3((unsigned)tokens, (unsigned)(split ? runs : 1)), dim3(THREADS), smem, s, 1, (T*)out,
                          (const T*)q, (const T*)k_pages, (const T*)v_pages, head_mix, positions, entry_of_token,
                          block_table, table_width, page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
-                         out_scale, split, partial, status);
+                         out_scale, split, partial, kv_stage, status);
     if (rc || !split) return rc;
     return kipp_launch(attention_mix_merge_kernel<T>, dim3((unsigned)tokens), dim3(THREADS), 0, s, 1, (T*)out,
                        (const float*)partial, positions, n_q, v_dim, window, keep_first, runs, out_scale);

@@ -125,7 +125,7 @@ def test_polynorm_feed_forward_alone(name, layer, dtype):
 
 
 # ------------------------------------------------------------------ whole models
-LENGTH = {"P": 90, "Q": 131, "R": 230, "S": 70}
+LENGTH = {"P": 90, "Q": 131, "R": 230, "S": 70, "T": 100}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

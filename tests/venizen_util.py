@@ -66,9 +66,15 @@ CONFIGS = {
           "layers": [parallel_layer(attention(3, 1, 6, 5, 9, 2, 2, scale=0.7), retention(1, 10, 3, [0.8], 6), 50),
                      delta_layer(2, 6, 3, None)],
           "loop": {"start": 0, "stop": 2, "times": 2}},
+    # four key/value heads of 128: in 32-bit a tile's keys and values of all of them do not fit in
+    # shared memory at once, so the attention walks them in passes
+    "T": {"architecture": "Venizen", "vocab": 128, "width": 64, "norm": {"eps": 1e-6},
+          "layers": [parallel_layer(attention(4, 4, 128, 128, 40, 2, 128, scale=0.2), retention(1, 16, 16, [0.9], 16), None)],
+          "loop": {"start": 0, "stop": 0, "times": 1}},
 }
 INIT = {"P": dict(seed=3, sigma=0.15, norm_jitter=0.2), "Q": dict(seed=5, sigma=0.12, norm_jitter=0.1),
-        "R": dict(seed=9, sigma=0.08, norm_jitter=0.15), "S": dict(seed=12, sigma=0.2, norm_jitter=0.1)}
+        "R": dict(seed=9, sigma=0.08, norm_jitter=0.15), "S": dict(seed=12, sigma=0.2, norm_jitter=0.1),
+        "T": dict(seed=14, sigma=0.1, norm_jitter=0.1)}
 
 _tmp = tempfile.TemporaryDirectory(prefix="kipp_b200_venizen_")
 
