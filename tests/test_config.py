@@ -103,11 +103,13 @@ def test_presets_are_data_and_valid():
     preset has the sizes of the 4B benchmark configuration."""
     from kipp_b200.config import config_from_dict, load_preset, preset_names
     names = preset_names()
-    assert {"tiny-a", "tiny-b", "qwen3-4b", "qwen3-8b", "qwen3-32b"} <= set(names)
+    assert {"tiny-a", "tiny-b", "venizen-tiny", "qwen3-4b", "qwen3-8b", "qwen3-32b"} <= set(names)
     for name in names:
         cfg_dict, init = load_preset(name)
-        cfg = config_from_dict(cfg_dict)
-        assert cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        cfg = config_from_dict(cfg_dict)                     # the architecture's own checks run here
+        if cfg.architecture == "Qwen3ForCausalLM":
+            assert cfg.num_attention_heads % cfg.num_key_value_heads == 0
+        assert cfg.vocab_size > 0 and cfg.hidden_size > 0
         assert init["seed"] >= 0 and init["sigma"] > 0
     cfg = config_from_dict(load_preset("qwen3-4b")[0])
     assert (cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads,
