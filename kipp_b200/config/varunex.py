@@ -1,0 +1,64 @@
+"""Configuration of the Varunex decoder, from its ``config.json`` keys.
+
+The file is nested: ``layers`` lists the layers one by one (``type`` ``mlstm``,
+``latent_attention`` or ``attention``, the mixer's sizes and constants under
+``mixer``, the feed-forward under ``mlp`` or null), ``norm.eps`` is the eps of
+every norm, and ``vocab`` / ``width`` are the two global sizes.  The model class
+is named by the key ``architecture``.  The checks are the host core's
+(csrc/host/varunex.hpp); this class keeps the keys as they are.
+"""
+from __future__ import annotations
+
+import copy
+import dataclasses
+import json
+from typing import Any
+
+from .base import ConfigError, ModelConfig, architecture_name
+
+
+@dataclasses.dataclass(frozen=True)
+class VarunexConfig(ModelConfig):
+    vocab: int = 0
+    width: int = 0
+    norm: dict = dataclasses.field(default_factory=dict)
+    layers: tuple = ()
+
+    @classmethod
+    def from_dict(cls, data: dict[str, Any]) -> "VarunexConfig":
+        if not isinstance(data, dict):
+            raise ConfigError("config.json must hold a JSON object")
+        for key in ("vocab", "width", "norm", "layers"):
+            if key not in data:
+                raise ConfigError(f"config.json lacks required key {key!r}")
+        if not isinstance(data["layers"], (list, tuple)):
+            raise ConfigError("config key 'layers' must be a list of layers")
+        config = cls(architecture=architecture_name(data), vocab=data["vocab"], width=data["width"],
+                     norm=copy.deepcopy(data["norm"]), layers=tuple(copy.deepcopy(list(data["layers"]))))
+        config.validate()
+        return config
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+                "norm": copy.deepcopy(self.norm), "layers": copy.deepcopy(list(self.layers))}
+
+    # what code that sizes a run asks of any configuration
+    @property
+    def vocab_size(self) -> int:
+        return self.vocab
+
+    @property
+    def hidden_size(self) -> int:
+        return self.width
+
+    @property
+    def initializer_range(self) -> float:
+        return 0.02
+
+    def normalized(self) -> dict:
+        """The keys after the host core's checks and defaults."""
+        from .. import native as N
+        return json.loads(N.text_result(N.lib().kipp_config_normalize, json.dumps(self.to_dict()).encode()))
+
+    def validate(self) -> None:
+        self.normalized()

@@ -16,6 +16,19 @@
 // every sum depends on the token's own position only: not on how the prompt was
 // cut, on the batch, or on the pages.
 //
+// Options beside the mix (MixExtras, all off by default), each of which needs all heads of a
+// query in one place or changes what a key row holds:
+//   sink            a learned number per head joins the softmax's denominator as e^sink: it has no
+//                   key and no value, is not scaled, and counts once (after the runs are merged);
+//   key_maps        every head has several score maps (n_q counts the maps, head by head); a key
+//                   row of a kv head holds key_maps keys of head_dim side by side, and all maps of
+//                   a head read the same values;
+//   diff            with two maps per head the output is o = a1 - lambda a2, divided by its root
+//                   mean square over the value size and multiplied by diff_scale;
+//   values_in_keys  the value of a key is the first v_dim elements of its key row (a latent that is
+//                   both key and value; there are no value pages);
+//   gate            head h of token t is multiplied by sigmoid(gate[t, gate_off + h]).
+//
 // attention_mix_kernel: one block per token (and, in steps of few tokens, per run of
 // SPLIT_TILES key tiles of that token: the runs' partial results -- maximum, sum and
 // unnormalised output per head -- are merged in run order by attention_mix_merge_kernel; how a
@@ -74,12 +87,67 @@ __device__ __forceinline__ void visible_runs(int pos, int window, int keep_first
 
 constexpr int SPLIT_TILES = 2;     // key tiles per run when a step's tokens are cut into runs
 
+// The layout is the host's AttentionExtras (kernels.hpp).
+struct MixExtras {
+    const float* sink;         // [n_q] or null
+    int key_maps;              // score maps per head (at least 1)
+    int values_in_keys;
+    int diff;                  // 1: two maps per head are combined (key_maps must be 2)
+    float lambda, diff_eps, diff_scale;
+    const void* gate;          // [tokens, ld_gate] in the compute type, or null
+    long long ld_gate;
+    int gate_off;
+};
+
+__device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// The factor that turns a head's unnormalised sum (maximum m, sum of weights l) into its output:
+// with a sink the denominator also holds e^sink.
+__device__ __forceinline__ float softmax_factor(float m, float l, const float* sink, int h) {
+    if (sink == nullptr) return l > 0.f ? 1.0f / l : 0.f;
+    const float s = sink[h], top = fmaxf(m, s);
+    const float w = m == -INFINITY ? 0.f : expf(m - top);
+    return w / (l * w + expf(s - top));
+}
+
+// heads [n_q][v_dim] (float32, shared memory, already divided by their denominators) -> the
+// token's row of the output: the maps of a head combined, the gate, the scale.
+template <typename T>
+__device__ __forceinline__ void finish_heads(T* __restrict__ out, const float* __restrict__ heads, int t, int n_q,
+                                             int v_dim, float out_scale, const MixExtras& ex, int threads) {
+    const T* gate = static_cast<const T*>(ex.gate);
+    if (!ex.diff) {
+        for (int e = threadIdx.x; e < n_q * v_dim; e += threads) {
+            float y = heads[e] * out_scale;
+            if (gate != nullptr) y *= sigmoid_(to_f32(gate[(size_t)t * ex.ld_gate + ex.gate_off + e / v_dim]));
+            out[(size_t)t * n_q * v_dim + e] = from_f32<T>(y);
+        }
+        return;
+    }
+    const int lane = threadIdx.x & 31, n_out = n_q / 2;
+    for (int h = threadIdx.x >> 5; h < n_out; h += threads >> 5) {
+        const float* a1 = heads + (size_t)(2 * h) * v_dim;
+        const float* a2 = a1 + v_dim;
+        float ss = 0.f;
+        for (int d = lane; d < v_dim; d += 32) {
+            const float o = fmaf(-ex.lambda, a2[d], a1[d]);
+            ss = fmaf(o, o, ss);
+        }
+        ss = warp_sum(ss);
+        float f = ex.diff_scale * out_scale / sqrtf(ss / (float)v_dim + ex.diff_eps);
+        if (gate != nullptr) f *= sigmoid_(to_f32(gate[(size_t)t * ex.ld_gate + ex.gate_off + h]));
+        for (int d = lane; d < v_dim; d += 32)
+            out[((size_t)t * n_out + h) * v_dim + d] = from_f32<T>(fmaf(-ex.lambda, a2[d], a1[d]) * f);
+    }
+}
+
 // Rows of `elems` elements from the pages into shared memory (row stride ld), 16 bytes at a time
 // where the sizes allow; rows of keys that are not visible become zeros.
 template <typename T>
 __device__ __forceinline__ void stage_rows(T* __restrict__ dst, int ld, const T* __restrict__ pages, int elems,
                                            int n_kv, int g0, int ng, int page_size, const int* pg, const int* sl,
                                            bool vec) {
+    // (a row of the pages has `elems` elements)
     // kv heads g0 .. g0 + ng - 1; row (g - g0) * KT + key of dst
     constexpr int VEC = Vec<T>::N;
     if (vec) {
@@ -111,11 +179,13 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
                      const int* __restrict__ positions, const int* __restrict__ entry_of_token,
                      const int* __restrict__ block_table, int table_width, int page_size, int n_q, int n_kv,
                      int head_dim, int v_dim, float scale, int window, int keep_first, float out_scale,
-                     int split, float* __restrict__ partial, int kv_stage, int* __restrict__ status) {
+                     int split, float* __restrict__ partial, int kv_stage, int* __restrict__ status,
+                     const MixExtras ex) {
     // kv_stage: kv heads whose keys (then values) of a tile are in shared memory at a time; all of
     // them where they fit, else the tile is walked in passes over groups of kv heads
     extern __shared__ __align__(16) float smem[];
-    const int ldk = head_dim + row_pad<T>(), ldv = v_dim + row_pad<T>();
+    const int maps = ex.key_maps, k_row = maps * head_dim;          // a key row holds the keys of all maps
+    const int ldk = k_row + row_pad<T>(), ldv = v_dim + row_pad<T>();
     float* qs = smem;                              // [n_q][head_dim]
     float* mix = qs + n_q * head_dim;              // [n_q][n_q]
     float* sraw = mix + n_q * n_q;                 // [n_q][KT]
@@ -144,9 +214,10 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
     if (it0 >= n_tiles) return;                    // this token has fewer runs than the step's longest
     const int it1 = split ? min(n_tiles, it0 + SPLIT_TILES) : n_tiles;
     const int* table = block_table + (size_t)entry_of_token[t] * table_width;
-    const int group = n_q / n_kv;
+    const int group = n_q / n_kv;                                   // score maps per kv head
     constexpr int VEC = Vec<T>::N;
-    const bool kvec = head_dim % VEC == 0 && (((uintptr_t)k_pages) & 15) == 0;
+    const bool kvec = k_row % VEC == 0 && (((uintptr_t)k_pages) & 15) == 0;
+    const bool kdot = kvec && head_dim % VEC == 0;
     const bool vvec = v_dim % VEC == 0 && (((uintptr_t)v_pages) & 15) == 0;
 
     for (int i = tid; i < n_q * head_dim; i += THREADS) qs[i] = to_f32(q[(size_t)t * n_q * head_dim + i]);
@@ -174,15 +245,16 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
         for (int g0 = 0; g0 < n_kv; g0 += kv_stage) {
             const int ng = min(kv_stage, n_kv - g0);
             if (g0 > 0) __syncthreads();                           // the pass before has read its keys
-            stage_rows(ktile, ldk, k_pages, head_dim, n_kv, g0, ng, page_size, pg, sl, kvec);
-            if (g0 + ng >= n_kv && kv_stage >= n_kv)               // one pass: the values can come at once
+            stage_rows(ktile, ldk, k_pages, k_row, n_kv, g0, ng, page_size, pg, sl, kvec);
+            if (g0 + ng >= n_kv && kv_stage >= n_kv && !ex.values_in_keys)   // one pass: the values can come at once
                 stage_rows(vtile, ldv, v_pages, v_dim, n_kv, 0, n_kv, page_size, pg, sl, vvec);
             cp_async_commit();
             cp_async_wait<0>();
             __syncthreads();
             for (int idx = tid; idx < ng * group * KT; idx += THREADS) {
                 const int hl = idx / KT, jj = idx % KT, h = g0 * group + hl;
-                sraw[h * KT + jj] = dot_row(qs + h * head_dim, ktile + ((size_t)(hl / group) * KT + jj) * ldk, head_dim, kvec) * scale;
+                sraw[h * KT + jj] = dot_row(qs + h * head_dim, ktile + ((size_t)(hl / group) * KT + jj) * ldk + (h % maps) * head_dim,
+                                            head_dim, kdot) * scale;
             }
         }
         __syncthreads();
@@ -224,13 +296,15 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
             }
             for (int el = tid; el < ng * group * v_dim; el += THREADS) {
                 const int hl = el / v_dim, d = el % v_dim, h = g0 * group + hl, e = h * v_dim + d;
-                const T* vcol = vtile + (size_t)(hl / group) * KT * ldv + d;
+                // (values that are the head of their key row are read where the keys were staged)
+                const int ldx = ex.values_in_keys ? ldk : ldv;
+                const T* vcol = (ex.values_in_keys ? ktile : vtile) + (size_t)(hl / group) * KT * ldx + d;
                 const float* ph = pw + h * KT;
                 float a0 = acc[e] * corr[h], a1 = 0.f;
 #pragma unroll 8
                 for (int jj = 0; jj < KT; jj += 2) {
-                    a0 = fmaf(ph[jj], to_f32(vcol[(size_t)jj * ldv]), a0);
-                    a1 = fmaf(ph[jj + 1], to_f32(vcol[(size_t)(jj + 1) * ldv]), a1);
+                    a0 = fmaf(ph[jj], to_f32(vcol[(size_t)jj * ldx]), a0);
+                    a1 = fmaf(ph[jj + 1], to_f32(vcol[(size_t)(jj + 1) * ldx]), a1);
                 }
                 acc[e] = a0 + a1;
             }
@@ -248,16 +322,20 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
         return;
     }
     for (int e = tid; e < n_q * v_dim; e += THREADS) {
-        const float l = l_run[e / v_dim];
-        out[(size_t)t * n_q * v_dim + e] = from_f32<T>(l > 0.f ? acc[e] / l * out_scale : 0.f);
+        const int h = e / v_dim;
+        acc[e] *= softmax_factor(m_run[h], l_run[h], ex.sink, h);
     }
+    __syncthreads();
+    finish_heads(out, acc, t, n_q, v_dim, out_scale, ex, THREADS);
 }
 
 // The runs of a token merged in run order: o = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M).
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 attention_mix_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, const int* __restrict__ positions,
-                           int n_q, int v_dim, int window, int keep_first, int max_runs, float out_scale) {
+                           int n_q, int v_dim, int window, int keep_first, int max_runs, float out_scale,
+                           const MixExtras ex) {
+    extern __shared__ __align__(16) float merged[];                 // [n_q][v_dim]
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, pos = positions[t];
@@ -277,25 +355,29 @@ attention_mix_merge_kernel(T* __restrict__ out, const float* __restrict__ partia
             l = fmaf(p[1], w, l);
             o = fmaf(p[2 + d], w, o);
         }
-        out[(size_t)t * n_q * v_dim + e] = from_f32<T>(l > 0.f ? o / l * out_scale : 0.f);
+        merged[e] = o * softmax_factor(m, l, ex.sink, h);
     }
+    __syncthreads();
+    finish_heads(out, merged, t, n_q, v_dim, out_scale, ex, THREADS);
 }
 
 template <typename T>
 int launch_mix(void* out, const void* q, const void* k_pages, const void* v_pages, const float* head_mix,
                const int* positions, const int* entry_of_token, const int* block_table, int table_width, int page_size,
                int tokens, int n_q, int n_kv, int head_dim, int v_dim, float scale, int window, int keep_first,
-               float out_scale, int runs, float* partial, int* status, cudaStream_t s) {
+               float out_scale, int runs, float* partial, int* status, const MixExtras& ex, cudaStream_t s) {
     const size_t head_floats = ((size_t)n_q * head_dim + (size_t)n_q * n_q + 2 * (size_t)n_q * KT + (size_t)n_q * v_dim +
                                 3 * (size_t)n_q + 2 * KT + 3) / 4 * 4;
     // kv heads staged at a time: all of them within about 100 KB of shared memory, else as many as fit
-    const size_t per_kv = (size_t)KT * ((size_t)head_dim + v_dim + 2 * row_pad<T>()) * sizeof(T);
+    const size_t per_kv = (size_t)KT * ((size_t)ex.key_maps * head_dim + row_pad<T>() +
+                                        (ex.values_in_keys ? 0 : v_dim + row_pad<T>())) * sizeof(T);
     const size_t head_bytes = head_floats * sizeof(float), budget = 100 * 1024;
     int kv_stage = n_kv;
     if (head_bytes + per_kv * n_kv > budget)
         kv_stage = (int)std::max<size_t>(1, std::min<size_t>((size_t)n_kv, budget > head_bytes ? (budget - head_bytes) / per_kv : 1));
     const size_t smem = head_bytes + per_kv * kv_stage;
     if (smem > 200 * 1024) return KIPP_ERR_ARG;
+    if (ex.values_in_keys && kv_stage < n_kv) return KIPP_ERR_ARG;     // the keys of a tile must still be there
     auto kernel = attention_mix_kernel<T>;
     static size_t allowed = 0;
     if (smem > 48 * 1024 && smem > allowed) {
@@ -307,10 +389,18 @@ int launch_mix(void* out, const void* q, const void* k_pages, const void* v_page
     int rc = kipp_launch(kernel, dim3((unsigned)tokens, (unsigned)(split ? runs : 1)), dim3(THREADS), smem, s, 1, (T*)out,
                          (const T*)q, (const T*)k_pages, (const T*)v_pages, head_mix, positions, entry_of_token,
                          block_table, table_width, page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
-                         out_scale, split, partial, kv_stage, status);
+                         out_scale, split, partial, kv_stage, status, ex);
     if (rc || !split) return rc;
-    return kipp_launch(attention_mix_merge_kernel<T>, dim3((unsigned)tokens), dim3(THREADS), 0, s, 1, (T*)out,
-                       (const float*)partial, positions, n_q, v_dim, window, keep_first, runs, out_scale);
+    const size_t merge_smem = (size_t)n_q * v_dim * sizeof(float);
+    auto merge = attention_mix_merge_kernel<T>;
+    static size_t merge_allowed = 0;
+    if (merge_smem > 48 * 1024 && merge_smem > merge_allowed) {
+        cudaError_t e = cudaFuncSetAttribute(merge, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem);
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+        merge_allowed = merge_smem;
+    }
+    return kipp_launch(merge, dim3((unsigned)tokens), dim3(THREADS), merge_smem, s, 1, (T*)out,
+                       (const float*)partial, positions, n_q, v_dim, window, keep_first, runs, out_scale, ex);
 }
 
 // ---------------------------------------------------------------------------
@@ -677,23 +767,42 @@ extern "C" long long kipp_attention_mix_scratch_floats(int tokens, int runs, int
     return runs > 1 ? (long long)tokens * runs * n_q * (v_dim + 2) : 0;
 }
 
-extern "C" int kipp_attention_mix(void* out, const void* q, const void* k_pages, const void* v_pages, int dtype,
-                                  const float* head_mix, const int* positions, const int* entry_of_token,
-                                  const int* block_table, int table_width, int page_size, int tokens, int n_q,
-                                  int n_kv, int head_dim, int v_dim, float scale, int window, int keep_first,
-                                  float out_scale, int runs, float* partial, int* status, void* stream) {
+// `extras`: the options of MixExtras, or null for none.  n_q counts score maps (heads x key_maps);
+// out is [tokens, n_q, v_dim], or [tokens, n_q / 2, v_dim] when the maps of a head are combined.
+extern "C" int kipp_attention_mix_ex(void* out, const void* q, const void* k_pages, const void* v_pages, int dtype,
+                                     const float* head_mix, const int* positions, const int* entry_of_token,
+                                     const int* block_table, int table_width, int page_size, int tokens, int n_q,
+                                     int n_kv, int head_dim, int v_dim, float scale, int window, int keep_first,
+                                     float out_scale, int runs, float* partial, const void* extras, int* status,
+                                     void* stream) {
     if (tokens <= 0) return 0;
     if (head_dim <= 0 || v_dim <= 0 || n_q <= 0 || n_kv <= 0 || n_q % n_kv || page_size <= 0 || window < 0 ||
         keep_first < 0 || runs < 1 || (runs > 1 && partial == nullptr))
+        return KIPP_ERR_ARG;
+    MixExtras ex = {};
+    ex.key_maps = 1;
+    if (extras != nullptr) ex = *static_cast<const MixExtras*>(extras);
+    if (ex.key_maps < 1 || (n_q / n_kv) % ex.key_maps || (ex.diff && ex.key_maps != 2) ||
+        (ex.values_in_keys && v_dim > ex.key_maps * head_dim))
         return KIPP_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == KIPP_DT_F32)
         return launch_mix<float>(out, q, k_pages, v_pages, head_mix, positions, entry_of_token, block_table, table_width,
                                  page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, runs,
-                                 partial, status, s);
+                                 partial, status, ex, s);
     if (dtype == KIPP_DT_BF16)
         return launch_mix<bf16>(out, q, k_pages, v_pages, head_mix, positions, entry_of_token, block_table, table_width,
                                 page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, runs,
-                                partial, status, s);
+                                partial, status, ex, s);
     return KIPP_ERR_DTYPE;
+}
+
+extern "C" int kipp_attention_mix(void* out, const void* q, const void* k_pages, const void* v_pages, int dtype,
+                                  const float* head_mix, const int* positions, const int* entry_of_token,
+                                  const int* block_table, int table_width, int page_size, int tokens, int n_q,
+                                  int n_kv, int head_dim, int v_dim, float scale, int window, int keep_first,
+                                  float out_scale, int runs, float* partial, int* status, void* stream) {
+    return kipp_attention_mix_ex(out, q, k_pages, v_pages, dtype, head_mix, positions, entry_of_token, block_table,
+                                 table_width, page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
+                                 out_scale, runs, partial, nullptr, status, stream);
 }

@@ -1,4 +1,4 @@
-// Embedding gather and RMSNorm.
+// Embedding gather, RMSNorm, layer norm, PolyNorm and element-wise activations.
 //
 // Reference counterparts: embed_kernel (cuda/kipp_kernels.cu:35) handles one
 // token per launch, rms_norm_kernel (cuda/kipp_kernels.cu:44) one row in one
@@ -217,4 +217,93 @@ extern "C" int kipp_add_f32(float* x, const float* y, long long n, void* stream)
     const long long blocks = (n + 255) / 256;
     if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
     return kipp_launch(add_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, x, y, n);
+}
+
+// ---------------------------------------------------------------------------
+// Layer norm with weight and bias: y[r, i] = (x[src(r), i] - mean) / sqrt(var + eps) * w[i] + b[i],
+// var = the mean of the squared deviations (two passes over the row, which a block keeps in
+// shared memory), all of it float32.  `rows`, when not null, gathers the input rows; b may be null.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+layernorm_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* __restrict__ w,
+                 const float* __restrict__ b, const int* __restrict__ rows, int size, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* src = x + (size_t)(rows ? rows[r] : r) * size;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float v = src[i];
+        row[i] = v;
+        s += v;
+    }
+    const float mean = block_sum(s, scratch) / (float)size;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float d = row[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)size + eps);
+    TO* dst = out + (size_t)r * size;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float y = (row[i] - mean) * inv * w[i];
+        dst[i] = from_f32<TO>(b ? y + b[i] : y);
+    }
+}
+
+extern "C" int kipp_layernorm(void* out, int out_dtype, const float* x, const float* w, const float* b,
+                              const int* rows, int n_rows, int size, float eps, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (size <= 0 || size > 48 * 1024 / 4 || w == nullptr) return KIPP_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = size >= 1024 ? 256 : 128;
+    const size_t smem = (size_t)size * sizeof(float);
+    if (out_dtype == KIPP_DT_F32)
+        return kipp_launch(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, s, 1, (float*)out, x, w, b, rows,
+                           size, eps);
+    if (out_dtype == KIPP_DT_BF16)
+        return kipp_launch(layernorm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, s, 1, (bf16*)out, x, w, b, rows,
+                           size, eps);
+    return KIPP_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// Activations applied element by element to z [rows, n] in the compute type, arithmetic in
+// float32: 0 relu, 1 the square of relu, 2 gelu with the tanh form
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 3 silu.
+__device__ __forceinline__ float activation_value(float z, int kind) {
+    switch (kind) {
+    case 0: return fmaxf(z, 0.f);
+    case 1: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+    default: return z / (1.0f + expf(-z));
+    }
+}
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ out, long long ld_out, const T* __restrict__ z, long long ld_z,
+                                  int rows, int n, int kind) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * n) return;
+    const long long r = i / n, c = i % n;
+    out[r * ld_out + c] = from_f32<T>(activation_value(to_f32(z[r * ld_z + c]), kind));
+}
+
+extern "C" int kipp_activation(void* out, long long ld_out, const void* z, long long ld_z, int dtype, int rows,
+                               int n, int kind, void* stream) {
+    if (rows <= 0 || n <= 0) return 0;
+    if (kind < 0 || kind > 3) return KIPP_ERR_ARG;
+    const long long total = (long long)rows * n, blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(activation_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, 1, (float*)out, ld_out,
+                           (const float*)z, ld_z, rows, n, kind);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(activation_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, 1, (bf16*)out, ld_out,
+                           (const bf16*)z, ld_z, rows, n, kind);
+    return KIPP_ERR_DTYPE;
 }

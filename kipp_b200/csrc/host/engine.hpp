@@ -14,8 +14,10 @@
 #include "cache_core.h"
 #include "parts.hpp"
 #include "recurrent_parts.hpp"
+#include "latent_parts.hpp"
 #include "qwen3.hpp"
 #include "venizen.hpp"
+#include "varunex.hpp"
 
 namespace kipp {
 
@@ -335,8 +337,32 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
                  fold_input(ctx, fold_in));
         void* q = ctx.workspace->buffer("q", (size_t)T * q_dim_ * es);
         const int write = (run.writes_cache ? 1 : 0) | (ctx.kv_round_bf16 && ctx.dtype == F32 ? 2 : 0);
-        ops.qk_norm_rope_write(qkv, qkv_cols, q, cache, ctx.dtype, qn, kn, norm_dtype_, eps_, cos_sin, rot, m.positions,
-                               m.entry_of_token, T, heads_, kv_heads_, head_dim_, write, v_dim_);
+        AttentionExtras extras;
+        if (segments_) {
+            // biases and score maps: every map of every head is a head of head_dim for the bias and
+            // the rotation; the maps of a key head go side by side into one row of the key pages
+            HeadSegment seg[3];
+            seg[0].src_off = 0; seg[0].heads = heads_ * maps_; seg[0].dim = head_dim_; seg[0].src_stride = head_dim_;
+            seg[0].rot = rot; seg[0].cos_sin = cos_sin; seg[0].bias = q_bias_;
+            seg[0].target = 0; seg[0].dst = q; seg[0].ld_dst = q_dim_; seg[0].dst_stride = head_dim_;
+            seg[1].src_off = q_dim_; seg[1].heads = kv_heads_ * maps_; seg[1].dim = head_dim_; seg[1].src_stride = head_dim_;
+            seg[1].rot = rot; seg[1].cos_sin = cos_sin; seg[1].bias = k_bias_;
+            seg[1].target = 1; seg[1].heads_per_row = maps_;
+            seg[2].src_off = q_dim_ + kv_dim_; seg[2].heads = kv_heads_; seg[2].dim = v_dim_; seg[2].src_stride = v_dim_;
+            seg[2].bias = v_bias_; seg[2].target = 2; seg[2].heads_per_row = 1;
+            ops.head_segments(qkv, qkv_cols, ctx.dtype, seg, 3, &cache, maps_ * head_dim_, v_dim_, kv_heads_, m.positions,
+                              m.entry_of_token, T, write, eps_);
+            extras.key_maps = maps_;
+            if (opt_.combine_maps) {
+                extras.diff = 1;
+                extras.lambda = lambda_;
+                extras.diff_eps = (float)opt_.combine_eps;
+                extras.diff_scale = (float)(1.0 - opt_.lambda_init);
+            }
+        } else {
+            ops.qk_norm_rope_write(qkv, qkv_cols, q, cache, ctx.dtype, qn, kn, norm_dtype_, eps_, cos_sin, rot, m.positions,
+                                   m.entry_of_token, T, heads_, kv_heads_, head_dim_, write, v_dim_);
+        }
         const int* tiles = nullptr;
         int n_tiles = 0;
         if (mix_planner_) {
@@ -346,9 +372,9 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
                 n_tiles = m.work_sizes.at(mix_planner_->key())[0] / 2;
             }
         }
-        ops.attention_mix(attn, q, cache, ctx.dtype, head_mix_, m.positions, m.entry_of_token, T, heads_, kv_heads_,
+        ops.attention_mix(attn, q, cache, ctx.dtype, head_mix_, m.positions, m.entry_of_token, T, heads_ * maps_, kv_heads_,
                           head_dim_, v_dim_, scale_, window_, window_ > 0 ? opt_.keep_first : 0,
-                          (float)opt_.output_scale, tiles, n_tiles, m.q_start, m.context_len);
+                          (float)opt_.output_scale, tiles, n_tiles, m.q_start, m.context_len, &extras);
         const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
         ops.gemm(residual, F32, hidden_, attn, o_dim_, w_o_, o_dim_, dtype_, T, hidden_, o_dim_, EPI_ADD, emit);
         fold_emitted(ctx, emit, hidden_);
@@ -538,7 +564,7 @@ inline void Engine::check_memory(const std::vector<TensorSpec>& specs) {
         auto mixers = plan_->layers[(size_t)run.layer].second->mixers();
         for (size_t s = 0; s < mixers.size(); ++s)
             if (auto cs = mixers[s]->cache_spec(); cs && seen.insert(cache_key(run.cache, (int)s)).second)
-                per_token += (size_t)cs->kv_heads * (cs->head_dim + cs->v_dim()) * es;
+                per_token += (size_t)cs->kv_heads * (cs->head_dim + cs->stored_v_dim()) * es;
     }
     size_t free_bytes = 0, total = 0;
     cuda_check(cudaMemGetInfo(&free_bytes, &total), "cudaMemGetInfo");
@@ -608,7 +634,7 @@ inline void Engine::build_cache() {
         g.cache_keys = by_spec[spec];
         g.n_pages = n_pages;
         g.cache_stride = (size_t)n_pages * spec.kv_heads * opt_.page_size * spec.head_dim * es;
-        g.value_stride = (size_t)n_pages * spec.kv_heads * opt_.page_size * spec.v_dim() * es;
+        g.value_stride = (size_t)n_pages * spec.kv_heads * opt_.page_size * spec.stored_v_dim() * es;
         const size_t bytes = g.cache_stride * g.cache_keys.size(), value_bytes = g.value_stride * g.cache_keys.size();
         g.k.reset(bytes, "key pages");
         g.v.reset(value_bytes, "value pages");
@@ -1366,7 +1392,7 @@ inline size_t Engine::weight_bytes() const {
 inline size_t Engine::cache_bytes_per_token() const {
     size_t n = 0;
     for (auto& g : groups_)
-        n += g.cache_keys.size() * g.spec.kv_heads * (g.spec.head_dim + g.spec.v_dim()) * dtype_size(dtype_);
+        n += g.cache_keys.size() * g.spec.kv_heads * (g.spec.head_dim + g.spec.stored_v_dim()) * dtype_size(dtype_);
     return n;
 }
 

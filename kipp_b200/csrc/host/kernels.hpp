@@ -75,6 +75,39 @@ struct PagedCacheView {
     int page_size = 0;
 };
 
+// Options of the mixed-head attention kernel beside the mix (the layout is the kernel library's
+// MixExtras, attention_mix.cu): a sink per head in the softmax's denominator, several score maps
+// per head that share their values (n_q then counts the maps), the combination of two maps into
+// one head, values that are the head of their key rows, a gate per head and token.
+struct AttentionExtras {
+    const float* sink = nullptr;
+    int key_maps = 1;
+    int values_in_keys = 0;
+    int diff = 0;
+    float lambda = 0.f, diff_eps = 0.f, diff_scale = 1.f;
+    const void* gate = nullptr;
+    long long ld_gate = 0;
+    int gate_off = 0;
+    bool any() const { return sink || key_maps != 1 || values_in_keys || diff || gate; }
+};
+
+// A run of heads in a projection row and what becomes of them (the layout is the kernel
+// library's HeadSegment, head_ops.cu).
+struct HeadSegment {
+    int src_off = 0, heads = 0, dim = 0, src_stride = 0;
+    int rot_off = 0, rot = 0;
+    int target = 0;                        // 0 activation rows, 1 key pages, 2 value pages
+    int dst_off = 0, dst_stride = 0;
+    int heads_per_row = 1;
+    const float* bias = nullptr;
+    const float* norm_w = nullptr;
+    const float* cos_sin = nullptr;
+    void* dst = nullptr;
+    long long ld_dst = 0;
+};
+
+enum Activation : int { ACT_RELU = 0, ACT_RELU_SQUARED = 1, ACT_GELU_TANH = 2, ACT_SILU = 3 };
+
 class Ops {
 public:
     cudaStream_t stream = nullptr;
@@ -100,6 +133,20 @@ public:
         using Fn = int (*)(void*, int, const float*, const void*, int, const int*, int, int, float, void*);
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_rmsnorm");
         run(f(out, out_dtype, x, weight, weight_dtype, rows, n_rows, size, eps, stream), "rmsnorm");
+    }
+
+    // out[r] = (x - mean) / sqrt(var + eps) * w + b over each row (bias may be null), float32 arithmetic.
+    void layernorm(void* out, int out_dtype, const float* x, const float* w, const float* b, const int* rows,
+                   int n_rows, int size, float eps) {
+        using Fn = int (*)(void*, int, const float*, const float*, const float*, const int*, int, int, float, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_layernorm");
+        run(f(out, out_dtype, x, w, b, rows, n_rows, size, eps, stream), "layernorm");
+    }
+    // out = act(z) element by element in the compute type (Activation).
+    void activation(void* out, long long ld_out, const void* z, long long ld_z, int dtype, int rows, int n, int kind) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_activation");
+        run(f(out, ld_out, z, ld_z, dtype, rows, n, kind, stream), "activation");
     }
 
     static bool gemm_tc_ok(int dtype, const void* a, long long lda, const void* w, long long ldw) {
@@ -231,22 +278,25 @@ public:
     void attention_mix(void* out, const void* q, const PagedCacheView& cache, int dtype, const float* head_mix,
                        const int* positions, const int* entry_of_token, int tokens, int n_q, int n_kv, int head_dim,
                        int v_dim, float scale, int window, int keep_first, float out_scale, const int* tiles = nullptr,
-                       int n_tiles = 0, const int* q_start = nullptr, const int* context_len = nullptr) {
+                       int n_tiles = 0, const int* q_start = nullptr, const int* context_len = nullptr,
+                       const AttentionExtras* extras = nullptr) {
         using Fn = int (*)(void*, const void*, const void*, const void*, int, const float*, const int*, const int*,
-                           const int*, int, int, int, int, int, int, int, float, int, int, float, int, float*, int*, void*);
+                           const int*, int, int, int, int, int, int, int, float, int, int, float, int, float*, const void*,
+                           int*, void*);
         using Fr = int (*)(int, int, int, int);
         using Fs = long long (*)(int, int, int, int);
         using Fo = int (*)(int, int, int, int);
         using Fm = int (*)(void*, const void*, const void*, const void*, const float*, const int*, int, const int*,
                            const int*, const int*, int, int, int, int, int, int, float, int, int, float, int*, void*);
-        static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix");
+        static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix_ex");
         static Fr runs_of = kernel_symbol<Fr>("attention_mix", "kipp_attention_mix_runs");
         static Fs scratch_of = kernel_symbol<Fs>("attention_mix", "kipp_attention_mix_scratch_floats");
         static Fo mma_ok = kernel_symbol<Fo>("attention_mix", "kipp_attention_mix_mma_ok");
         static Fm mma = kernel_symbol<Fm>("attention_mix", "kipp_attention_mix_mma");
         const bool aligned = (((uintptr_t)out | (uintptr_t)q | (uintptr_t)cache.k_pages | (uintptr_t)cache.v_pages) & 15) == 0;
-        if (dtype == BF16 && mix_tensor_core && tokens > MIX_MMA_MIN_TOKENS && tiles != nullptr && n_tiles > 0 && aligned &&
-            mma_ok(n_q, n_kv, head_dim, v_dim)) {
+        const bool plain = extras == nullptr || !extras->any();         // the tensor-core kernel has none of the options
+        if (dtype == BF16 && mix_tensor_core && plain && tokens > MIX_MMA_MIN_TOKENS && tiles != nullptr && n_tiles > 0 &&
+            aligned && mma_ok(n_q, n_kv, head_dim, v_dim)) {
             run(mma(out, q, cache.k_pages, cache.v_pages, head_mix, tiles, n_tiles, q_start, context_len, cache.block_table,
                     cache.table_width, cache.page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale,
                     status, stream),
@@ -260,8 +310,52 @@ public:
                                   : nullptr;
         run(f(out, q, cache.k_pages, cache.v_pages, dtype, head_mix, positions, entry_of_token, cache.block_table,
               cache.table_width, cache.page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
-              out_scale, runs, partial, status, stream),
+              out_scale, runs, partial, extras, status, stream),
             "attention_mix", runs > 1 ? 2 : 1);
+    }
+
+    // Bias, per-head norm, rotation of a part of the head and the way to an activation buffer or
+    // into the pages for up to four runs of heads of a projection row (head_ops.cu).
+    void head_segments(const void* src, long long ld_src, int dtype, const HeadSegment* segments, int n_segments,
+                       const PagedCacheView* cache, int k_row, int v_row, int n_kv, const int* positions,
+                       const int* entry_of_token, int tokens, int write_cache, float eps) {
+        using Fn = int (*)(const void*, long long, int, const void*, int, void*, void*, int, int, int, const int*,
+                           const int*, const int*, int, int, int, int, float, int*, void*);
+        static Fn f = kernel_symbol<Fn>("head_ops", "kipp_head_segments");
+        run(f(src, ld_src, dtype, segments, n_segments, cache ? cache->k_pages : nullptr, cache ? cache->v_pages : nullptr,
+              k_row, v_row, n_kv, positions, entry_of_token, cache ? cache->block_table : nullptr,
+              cache ? cache->table_width : 0, cache ? cache->page_size : 1, tokens, write_cache, eps, status, stream),
+            "head_segments");
+    }
+    // C[t, h, :] = W_h A[t, h, :] for every head: W_h [N, K] at w + h * w_head, rows of head h at
+    // a + h * a_head + t * lda, results at c + h * c_head + t * ldc.  bfloat16 products of many
+    // tokens whose operands the tensor-core kernel takes run there, head by head; else CUDA cores.
+    void head_matmul(void* c, long long ldc, long long c_head, const void* a, long long lda, long long a_head,
+                     const void* w, long long w_head, int dtype, int M, int N, int K, int heads) {
+        const size_t es = dtype_size(dtype);
+        bool tc = dtype == BF16 && M >= HEAD_MATMUL_TC_MIN_TOKENS && K % 8 == 0 && ldc % 8 == 0;
+        for (int h = 0; tc && h < heads; ++h)
+            tc = gemm_tc_ok(dtype, static_cast<const char*>(a) + (size_t)h * a_head * es, lda,
+                            static_cast<const char*>(w) + (size_t)h * w_head * es, K) &&
+                 ((uintptr_t)(static_cast<char*>(c) + (size_t)h * c_head * es) & 15) == 0;
+        if (tc) {
+            for (int h = 0; h < heads; ++h)
+                gemm(static_cast<char*>(c) + (size_t)h * c_head * es, dtype, ldc,
+                     static_cast<const char*>(a) + (size_t)h * a_head * es, lda,
+                     static_cast<const char*>(w) + (size_t)h * w_head * es, K, dtype, M, N, K, EPI_STORE);
+            return;
+        }
+        using Fn = int (*)(void*, const void*, const void*, int, int, int, int, int, long long, long long, long long,
+                           long long, long long, void*);
+        static Fn f = kernel_symbol<Fn>("head_ops", "kipp_head_matmul");
+        run(f(c, a, w, dtype, M, N, K, heads, lda, a_head, w_head, ldc, c_head, stream), "head_matmul");
+    }
+    static constexpr int HEAD_MATMUL_TC_MIN_TOKENS = 256;
+    // out[h] = in[h]^T for `heads` row-major matrices of [rows, cols]
+    void transpose_heads(void* out, const void* in, int dtype, int heads, int rows, int cols) {
+        using Fn = int (*)(void*, const void*, int, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("head_ops", "kipp_transpose_heads");
+        run(f(out, in, dtype, heads, rows, cols, stream), "transpose_heads");
     }
 
     // Whether the recurrent scan kernels take heads of these sizes.
@@ -270,10 +364,39 @@ public:
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
         return f(dim, v_dim, delta ? 1 : 0) != 0;
     }
-    float* recurrent_scratch(int tokens, int heads, int dim, int v_dim, bool delta) {
+    // kind: 0 retention, 1 delta rule, 2 gated memory
+    float* recurrent_scratch(int tokens, int heads, int dim, int v_dim, int kind) {
         using Fn = long long (*)(int, int, int, int, int);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scratch_floats");
-        return workspace->get<float>("recurrent_scratch", (size_t)f(tokens, heads, dim, v_dim, delta ? 1 : 0));
+        return workspace->get<float>("recurrent_scratch", (size_t)f(tokens, heads, dim, v_dim, kind));
+    }
+    static bool gated_memory_ok(int dim, int v_dim) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
+        return f(dim, v_dim, 2) != 0;
+    }
+    // float32 values of one request slot of the gated memory's state
+    static long long gated_memory_state_floats(int heads, int dim, int v_dim) {
+        using Fn = long long (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_gated_memory_state_floats");
+        return f(heads, dim, v_dim);
+    }
+    // The matrix memory with exponential gates held stable by a running maximum (recurrent.cu):
+    // m_t = max(f_t + m_{t-1}, i_t), S_t = e^(f_t + m_{t-1} - m_t) S_{t-1} + e^(i_t - m_t) k_t v_t^T, n_t alike,
+    // o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6); then root-mean-square division, weight, gate.
+    void gated_memory_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int q_off,
+                           int k_off, int v_off, int g_off, int i_off, int f_off, const float* i_bias,
+                           const float* f_bias, const float* norm_w, float* state, const int* q_start, const int* slots,
+                           int entries, int tokens, int heads, int dim, int v_dim, float gate_cap, float q_scale,
+                           float eps, float out_scale, int gate) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, int, int, const float*,
+                           const float*, const float*, float*, const int*, const int*, int, int, int, int, int, float,
+                           float, float, float, int, float*, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_gated_memory_scan");
+        float* scratch = recurrent_scratch(tokens, heads, dim, v_dim, 2);
+        run(f(out, ld_out, proj, ld_proj, dtype, q_off, k_off, v_off, g_off, i_off, f_off, i_bias, f_bias, norm_w, state,
+              q_start, slots, entries, tokens, heads, dim, v_dim, gate_cap, q_scale, eps, out_scale, gate, scratch, stream),
+            "gated_memory_scan", 3);
     }
     // S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t over each entry's tokens, from the state in
     // its slot and back into it; q and k rotated by the step's table and k scaled; then per-head
@@ -286,7 +409,7 @@ public:
                            const float*, int, const int*, const int*, int, int, int, int, int, float, float, float, int,
                            float*, void*);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_retention_scan");
-        float* scratch = recurrent_scratch(tokens, heads, dim, v_dim, false);
+        float* scratch = recurrent_scratch(tokens, heads, dim, v_dim, 0);
         run(f(out, ld_out, proj, ld_proj, dtype, q_off, k_off, v_off, g_off, state, decay, cos_sin, rot, q_start, slots,
               entries, tokens, heads, dim, v_dim, k_scale, eps, out_scale, gate, scratch, stream),
             "retention_scan", 3);
@@ -301,7 +424,7 @@ public:
                            const float*, const float*, const float*, float*, const int*, const int*, int, int, int, int,
                            float, float, int, float*, void*);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_delta_rule_scan");
-        float* scratch = recurrent_scratch(tokens, heads, dim, dim, true);
+        float* scratch = recurrent_scratch(tokens, heads, dim, dim, 1);
         run(f(out, ld_out, proj, ld_proj, dtype, r_off, k_off, v_off, g_off, a_off, w_raw, ld_w, a_bias, w_bias, norm_w,
               state, q_start, slots, entries, tokens, heads, dim, eps, out_scale, gate, scratch, stream),
             "delta_rule_scan", 3);

@@ -38,11 +38,16 @@ struct LayerRun {
 // value_dim (0: as the keys).  window 0 keeps every key; a window of w keeps keys j with
 // pos - w < j <= pos and, beside them, the first keep_first positions of the sequence.  Runs
 // with equal specs share a group of the cache manager (own pool, own block tables, own
-// retention).
+// retention).  values_in_keys: a key row also holds its value (its first value_dim elements, a
+// latent that is both), so the group has no value pages.
 struct PagedKVSpec {
     int kv_heads = 0, head_dim = 0, window = 0, value_dim = 0, keep_first = 0;
+    bool values_in_keys = false;
     int v_dim() const { return value_dim > 0 ? value_dim : head_dim; }
-    auto key() const { return std::make_tuple(kv_heads, head_dim, window, v_dim(), window > 0 ? keep_first : 0); }
+    int stored_v_dim() const { return values_in_keys ? 0 : v_dim(); }     // elements of a row of the value pages
+    auto key() const {
+        return std::make_tuple(kv_heads, head_dim, window, v_dim(), window > 0 ? keep_first : 0, values_in_keys);
+    }
     bool operator==(const PagedKVSpec& o) const { return key() == o.key(); }
     bool operator<(const PagedKVSpec& o) const { return key() < o.key(); }
 };
@@ -344,8 +349,8 @@ private:
     std::map<std::string, Architecture> archs_;
 };
 
-void register_builtin_parts();           // parts.hpp, recurrent_parts.hpp
-void register_builtin_architectures();   // qwen3.hpp, venizen.hpp
+void register_builtin_parts();           // parts.hpp, recurrent_parts.hpp, latent_parts.hpp
+void register_builtin_architectures();   // qwen3.hpp, venizen.hpp, varunex.hpp
 
 inline void ensure_registered() {
     static std::once_flag once;

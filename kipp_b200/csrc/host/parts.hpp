@@ -1,6 +1,8 @@
-// The parts the library brings: token embedding, RMSNorm, rotary position encodings, causal
-// grouped-query attention over the paged cache, the SwiGLU feed-forward, the output head, the
-// pre-norm block, and the wrapper behind parts whose forward pass the caller supplies.  Each
+// The parts the library brings: token embedding, RMSNorm and layer norm, rotary position
+// encodings (plain, or with long wavelengths stretched), causal grouped-query attention over the
+// paged cache, the SwiGLU and the plain dense feed-forward, the output head, the pre-norm block and
+// the block whose sublayers share one norm, and the wrapper behind parts whose forward pass the
+// caller supplies.  Each
 // is registered under a kind name; a plan builds them from JSON objects of sizes and constants.
 #pragma once
 #include "model.hpp"
@@ -104,6 +106,48 @@ private:
     void* weight_ = nullptr;
 };
 
+// y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared deviations, computed in
+// float32; weight and bias are kept in float32.  `bias_name` empty: no bias.
+class LayerNorm : public Norm {
+public:
+    LayerNorm(int size, double eps, std::string weight_name, std::string bias_name)
+        : size_(size), eps_((float)eps), name_(std::move(weight_name)), bias_name_(std::move(bias_name)) {
+        if (size <= 0 || !(eps > 0)) fail(KIPP_E_CONFIG, "layernorm: size and eps must be positive");
+    }
+    void tensor_specs(const std::string& prefix, std::vector<TensorSpec>& out) const override {
+        TensorSpec s;
+        s.name = prefix + name_;
+        s.shape = {size_};
+        s.init = "near_one";
+        out.push_back(s);
+        if (!bias_name_.empty()) {
+            TensorSpec b;
+            b.name = prefix + bias_name_;
+            b.shape = {size_};
+            out.push_back(b);
+        }
+    }
+    void bind(Binder& b, const std::string& prefix) override {
+        weight_ = static_cast<float*>(b.allocate((size_t)size_ * sizeof(float), prefix + name_));
+        b.load(prefix + name_, weight_, F32, size_, 1, size_);
+        if (!bias_name_.empty()) {
+            bias_ = static_cast<float*>(b.allocate((size_t)size_ * sizeof(float), prefix + bias_name_));
+            b.load(prefix + bias_name_, bias_, F32, size_, 1, size_);
+        }
+    }
+    size_t weight_bytes() const override { return (size_t)size_ * sizeof(float) * (bias_name_.empty() ? 1 : 2); }
+    int size() const override { return size_; }
+    void forward(StepContext& ctx, const float* x, void* out, const int* rows, int n_rows) override {
+        ctx.ops->layernorm(out, ctx.dtype, x, weight_, bias_, rows, n_rows, size_, eps_);
+    }
+
+private:
+    int size_;
+    float eps_;
+    std::string name_, bias_name_;
+    float *weight_ = nullptr, *bias_ = nullptr;
+};
+
 // ---------------------------------------------------------------------------------------------
 // Rotations given by a table of frequencies: pair (i, i + rotary_dim/2) of a head turns by
 // position * inv_freq[i].
@@ -138,6 +182,28 @@ inline std::vector<float> rotary_frequencies(int rotary_dim, double theta, bool 
     for (int i = 0; i < rotary_dim / 2; ++i) {
         const float exponent = -(2.0f * (float)i) / (float)rotary_dim;
         f[(size_t)i] = (float)std::pow(base, exact ? -2.0 * (double)i / (double)rotary_dim : (double)exponent);
+    }
+    return f;
+}
+
+// Frequencies whose long wavelengths are stretched (the frequency scaling of Llama 3.1): with
+// the wavelength l = 2 pi / f, f stays where l < original / high, becomes f / factor where
+// l > original / low, and between the two is (1 - s) f / factor + s f with
+// s = (original / l - low) / (high - low).  Formed in double precision, rounded to float32 once.
+inline std::vector<float> stretched_frequencies(int rotary_dim, double theta, double factor, double low, double high,
+                                                double original) {
+    std::vector<float> f((size_t)rotary_dim / 2);
+    const double two_pi = 6.283185307179586476925286766559;
+    for (int i = 0; i < rotary_dim / 2; ++i) {
+        double v = std::pow(theta, -2.0 * (double)i / (double)rotary_dim);
+        const double wave = two_pi / v;
+        if (wave > original / low) {
+            v /= factor;
+        } else if (!(wave < original / high)) {
+            const double s = (original / wave - low) / (high - low);
+            v = (1.0 - s) * v / factor + s * v;
+        }
+        f[(size_t)i] = (float)v;
     }
     return f;
 }
@@ -391,13 +457,27 @@ inline std::map<std::string, std::string> tensor_names(const Json& j, std::map<s
 // the heads' scores before the softmax (head_mix: score_h <- sum_g M[h][g] score_g, a tensor
 // [heads, heads]); a factor on the mixer's output (output_scale).  With any of them the step runs
 // on the attention_mix kernel, which holds all heads of a query together.
+//
+// Further options of that path: biases of the q, k and v projections (bias); several score maps
+// per head (score_maps: q has heads x maps x head_dim rows, k kv_heads x maps x head_dim, laid out
+// head by head as [map 1, map 2, ...]; every map is rotated like a head and is an attention of its
+// own over the head's values); and, with two maps, their combination into one head
+// (combine_maps: o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + lambda_init,
+// four vectors of head_dim, then o / sqrt(mean(o^2) + combine_eps) times (1 - lambda_init)).
 struct AttentionOptions {
     int value_dim = 0, keep_first = 0;
     bool head_mix = false;
     double output_scale = 1.0;
+    bool bias = false;
+    int score_maps = 1;
+    bool combine_maps = false;
+    double lambda_init = 0.0, combine_eps = 1e-5;
     std::map<std::string, std::string> names = {{"q", "q_proj.weight"}, {"k", "k_proj.weight"}, {"v", "v_proj.weight"},
                                                 {"o", "o_proj.weight"}, {"q_norm", "q_norm.weight"},
-                                                {"k_norm", "k_norm.weight"}, {"head_mix", "head_mix.weight"}};
+                                                {"k_norm", "k_norm.weight"}, {"head_mix", "head_mix.weight"},
+                                                {"q_bias", "q_proj.bias"}, {"k_bias", "k_proj.bias"},
+                                                {"v_bias", "v_proj.bias"}, {"lq1", "lambda_q1"}, {"lk1", "lambda_k1"},
+                                                {"lq2", "lambda_q2"}, {"lk2", "lambda_k2"}};
 };
 
 class AttentionMixer : public Mixer {
@@ -417,11 +497,19 @@ public:
             fail(KIPP_E_CONFIG, "attention: rotary_dim must be even and at most head_dim");
         scale_ = scale ? (float)*scale : (float)(1.0 / std::sqrt((double)head_dim));
         v_dim_ = opt_.value_dim > 0 ? opt_.value_dim : head_dim;
-        q_dim_ = heads * head_dim;
-        kv_dim_ = kv_heads * head_dim;
+        maps_ = opt_.score_maps;
+        if (maps_ < 1) fail(KIPP_E_CONFIG, "attention: score_maps must be at least 1");
+        if (opt_.combine_maps && maps_ != 2) fail(KIPP_E_CONFIG, "attention: combine_maps needs two score maps");
+        if (opt_.combine_maps && !(opt_.combine_eps > 0)) fail(KIPP_E_CONFIG, "attention: combine_eps must be positive");
+        if (opt_.head_mix && maps_ != 1) fail(KIPP_E_CONFIG, "attention: head_mix and score_maps do not go together");
+        segments_ = opt_.bias || maps_ > 1;
+        if (segments_ && qk_norm_) fail(KIPP_E_CONFIG, "attention: q/k norm with biases or score maps is not supported");
+        q_dim_ = heads * maps_ * head_dim;
+        kv_dim_ = kv_heads * maps_ * head_dim;
         vv_dim_ = kv_heads * v_dim_;
         o_dim_ = heads * v_dim_;
-        mix_path_ = opt_.head_mix || (window_ > 0 && opt_.keep_first > 0) || v_dim_ != head_dim_ || opt_.output_scale != 1.0;
+        mix_path_ = opt_.head_mix || (window_ > 0 && opt_.keep_first > 0) || v_dim_ != head_dim_ ||
+                    opt_.output_scale != 1.0 || segments_;
     }
     void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
         auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
@@ -440,10 +528,18 @@ public:
             add("k_norm", {head_dim_}, "near_one");
         }
         if (opt_.head_mix) add("head_mix", {heads_, heads_}, "near_identity");
+        if (opt_.bias) {
+            add("q_bias", {q_dim_});
+            add("k_bias", {kv_dim_});
+            add("v_bias", {vv_dim_});
+        }
+        if (opt_.combine_maps)
+            for (const char* r : {"lq1", "lk1", "lq2", "lk2"}) add(r, {head_dim_});
         position_->tensor_specs(p, out);
     }
+    // (the maps of a key head lie side by side in one row of the key pages)
     std::optional<PagedKVSpec> cache_spec() const override {
-        return PagedKVSpec{kv_heads_, head_dim_, window_, v_dim_, window_ > 0 ? opt_.keep_first : 0};
+        return PagedKVSpec{kv_heads_, maps_ * head_dim_, window_, v_dim_, window_ > 0 ? opt_.keep_first : 0};
     }
     std::shared_ptr<WorkPlanner> planner(const DeviceInfo& dev, bool own_length) override {
         if (mix_path_) {                          // (entry, first token) per tile of its tensor-core prompt kernel
@@ -483,12 +579,38 @@ public:
             head_mix_ = static_cast<float*>(b.allocate((size_t)heads_ * heads_ * sizeof(float), hm));
             b.load(hm, head_mix_, F32, heads_, heads_, heads_);
         }
+        auto floats = [&](const char* role, int64_t n) {
+            float* d = static_cast<float*>(b.allocate((size_t)n * sizeof(float), p + opt_.names.at(role)));
+            b.load(p + opt_.names.at(role), d, F32, n, 1, n);
+            return d;
+        };
+        if (opt_.bias) {
+            q_bias_ = floats("q_bias", q_dim_);
+            k_bias_ = floats("k_bias", kv_dim_);
+            v_bias_ = floats("v_bias", vv_dim_);
+        }
+        if (opt_.combine_maps) {
+            // lambda is one number for the layer: formed once, in double precision
+            double dot[2] = {0.0, 0.0};
+            const char* roles[2][2] = {{"lq1", "lk1"}, {"lq2", "lk2"}};
+            for (int m = 0; m < 2; ++m) {
+                std::vector<float> a((size_t)head_dim_), c((size_t)head_dim_);
+                const float* da = floats(roles[m][0], head_dim_);
+                const float* dc = floats(roles[m][1], head_dim_);
+                cuda_check(cudaDeviceSynchronize(), "reading the lambda vectors");
+                cuda_check(cudaMemcpy(a.data(), da, a.size() * sizeof(float), cudaMemcpyDeviceToHost), "reading the lambda vectors");
+                cuda_check(cudaMemcpy(c.data(), dc, c.size() * sizeof(float), cudaMemcpyDeviceToHost), "reading the lambda vectors");
+                for (int i = 0; i < head_dim_; ++i) dot[m] += (double)a[(size_t)i] * (double)c[(size_t)i];
+            }
+            lambda_ = (float)(std::exp(dot[0]) - std::exp(dot[1]) + opt_.lambda_init);
+        }
         position_->bind(b, p);
     }
     size_t weight_bytes() const override {
         size_t n = ((size_t)(q_dim_ + kv_dim_ + vv_dim_) * hidden_ + (size_t)hidden_ * o_dim_) * dtype_size(dtype_);
         if (qk_norm_) n += 2 * (size_t)head_dim_ * dtype_size(norm_dtype_);
         if (opt_.head_mix) n += (size_t)heads_ * heads_ * sizeof(float);
+        if (opt_.bias) n += (size_t)(q_dim_ + kv_dim_ + vv_dim_) * sizeof(float);
         return n;
     }
     bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_qkv_, hidden_, w_qkv_, hidden_); }
@@ -503,9 +625,11 @@ private:
     AttentionOptions opt_;
     float scale_ = 1.f;
     int v_dim_ = 0, q_dim_ = 0, kv_dim_ = 0, vv_dim_ = 0, o_dim_ = 0, dtype_ = BF16, norm_dtype_ = F32;
-    bool mix_path_ = false;
+    bool mix_path_ = false, segments_ = false;
+    int maps_ = 1;
+    float lambda_ = 0.f;
     void *w_qkv_ = nullptr, *w_o_ = nullptr, *q_norm_ = nullptr, *k_norm_ = nullptr;
-    float* head_mix_ = nullptr;
+    float *head_mix_ = nullptr, *q_bias_ = nullptr, *k_bias_ = nullptr, *v_bias_ = nullptr;
     std::shared_ptr<AttentionPlanner> planner_;
     std::shared_ptr<MixTilePlanner> mix_planner_;
 };
@@ -556,6 +680,107 @@ public:
 private:
     int hidden_, inter_, dtype_ = BF16;
     void *w_gate_up_ = nullptr, *w_down_ = nullptr;
+};
+
+// Dense feed-forward with one up projection: x += W_down act(W_up n), act one of relu, relu_squared,
+// gelu_tanh, silu, applied in float32 to the projection's output.
+inline int activation_code(const std::string& a) {
+    if (a == "relu") return ACT_RELU;
+    if (a == "relu_squared") return ACT_RELU_SQUARED;
+    if (a == "gelu_tanh") return ACT_GELU_TANH;
+    if (a == "silu") return ACT_SILU;
+    fail(KIPP_E_CONFIG, "activation must be relu, relu_squared, gelu_tanh or silu, not '" + a + "'");
+}
+class DenseFeedForward : public FeedForward {
+public:
+    DenseFeedForward(int hidden, int intermediate, const std::string& activation, std::map<std::string, std::string> names)
+        : hidden_(hidden), inter_(intermediate), act_(activation_code(activation)), names_(std::move(names)) {
+        if (hidden <= 0 || intermediate <= 0) fail(KIPP_E_CONFIG, "dense_mlp: sizes must be positive");
+        ld_ = (inter_ + 7) / 8 * 8;
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        TensorSpec up, down;
+        up.name = p + names_.at("up");
+        up.shape = {inter_, hidden_};
+        down.name = p + names_.at("down");
+        down.shape = {hidden_, inter_};
+        out.push_back(up);
+        out.push_back(down);
+    }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        w_up_ = b.allocate((size_t)inter_ * hidden_ * es, p + names_.at("up"));
+        b.load(p + names_.at("up"), w_up_, dtype_, hidden_, inter_, hidden_);
+        // rows of W_down padded to a multiple of 8 elements (zeros beyond the feed-forward's size)
+        w_down_ = b.allocate((size_t)hidden_ * ld_ * es, p + names_.at("down"));
+        cuda_check(cudaMemset(w_down_, 0, (size_t)hidden_ * ld_ * es), "clearing a padded weight");
+        b.load(p + names_.at("down"), w_down_, dtype_, ld_, hidden_, inter_);
+    }
+    size_t weight_bytes() const override { return (size_t)2 * inter_ * hidden_ * dtype_size(dtype_); }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_up_, hidden_, w_up_, hidden_); }
+    void forward(StepContext& ctx, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        NormFold in, out;
+        void* z = ctx.workspace->buffer("ffn_up", (size_t)T * ld_ * ctx.element());
+        if (ld_ != inter_) cuda_check(cudaMemsetAsync(z, 0, (size_t)T * ld_ * ctx.element(), ctx.stream), "clearing the padding");
+        ctx.ops->gemm(z, ctx.dtype, ld_, h, hidden_, w_up_, hidden_, dtype_, T, inter_, hidden_, EPI_STORE, fold_input(ctx, in));
+        ctx.ops->activation(z, ld_, z, ld_, ctx.dtype, T, inter_, act_);
+        const NormFold* emit = fold_emit(ctx, out, hidden_);
+        ctx.ops->gemm(residual, F32, hidden_, z, ld_, w_down_, ld_, dtype_, T, hidden_, ld_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
+    }
+
+private:
+    int hidden_, inter_, act_, ld_ = 0, dtype_ = BF16;
+    std::map<std::string, std::string> names_;
+    void *w_up_ = nullptr, *w_down_ = nullptr;
+};
+
+// x += mixer(n) + ffn(n) with n = norm(x): ONE norm whose output both sublayers read.  A block
+// without a feed-forward (ffn null) has the mixer only.
+class ParallelBlock : public Block {
+public:
+    ParallelBlock(std::unique_ptr<Norm> norm, std::unique_ptr<Mixer> mixer, std::unique_ptr<FeedForward> ffn,
+                  std::vector<std::string> names)
+        : norm_(std::move(norm)), mixer_(std::move(mixer)), ffn_(std::move(ffn)), names_(std::move(names)) {
+        if (names_.size() != 3) fail(KIPP_E_CONFIG, "parallel_block: three name prefixes are needed");
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        norm_->tensor_specs(p + names_[0], out);
+        mixer_->tensor_specs(p + names_[1], out);
+        if (ffn_) ffn_->tensor_specs(p + names_[2], out);
+    }
+    void bind(Binder& b, const std::string& p) override {
+        norm_->bind(b, p + names_[0]);
+        mixer_->bind(b, p + names_[1]);
+        if (ffn_) ffn_->bind(b, p + names_[2]);
+    }
+    size_t weight_bytes() const override {
+        return norm_->weight_bytes() + mixer_->weight_bytes() + (ffn_ ? ffn_->weight_bytes() : 0);
+    }
+    bool graph_safe() const override { return norm_->graph_safe() && mixer_->graph_safe() && (!ffn_ || ffn_->graph_safe()); }
+    std::vector<Mixer*> mixers() override { return mixer_->parts(); }
+    void forward(StepContext& ctx, const LayerRun& run, float* x) override {
+        const int T = ctx.tokens();
+        // both sublayers read h, and both add to x: h must outlive the mixer, so no part may leave
+        // another norm's input in its place (emit_for stays null)
+        void* h = ctx.workspace->buffer("normed", (size_t)T * norm_->size() * ctx.element());
+        ctx.input_scale = RowScale{};
+        ctx.pending_norm = nullptr;
+        ctx.emit_for = nullptr;
+        ctx.emitted = false;
+        norm_->forward(ctx, x, h, nullptr, T);
+        mixer_->forward(ctx, run, 0, h, x);
+        if (ffn_) ffn_->forward(ctx, h, x);
+        ctx.emitted = false;
+    }
+
+private:
+    std::unique_ptr<Norm> norm_;
+    std::unique_ptr<Mixer> mixer_;
+    std::unique_ptr<FeedForward> ffn_;
+    std::vector<std::string> names_;
 };
 
 // x += mixer(norm1(x)); x += ffn(norm2(x)): the un-normed x is the residual stream
@@ -817,6 +1042,7 @@ inline std::unique_ptr<PositionEncoding> make_position(const Json& j, const Buil
     return Registry::get().make_as<PositionEncoding>(j, ctx, "a position encoding");
 }
 void register_recurrent_parts(Registry& r);     // recurrent_parts.hpp
+void register_latent_parts(Registry& r);        // latent_parts.hpp
 
 inline void register_builtin_parts() {
     Registry& r = Registry::get();
@@ -831,6 +1057,37 @@ inline void register_builtin_parts() {
     r.add_part_kind("rmsnorm", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<RMSNorm>((int)j.get("size").as_int(), j.get("eps").as_double(),
                                          j.get_string("weight_name", "weight"));
+    });
+    r.add_part_kind("layernorm", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
+        return std::make_unique<LayerNorm>((int)j.get("size").as_int(), j.get("eps").as_double(),
+                                           j.get_string("weight_name", "weight"), j.get_string("bias_name", "bias"));
+    });
+    r.add_part_kind("stretched_rotary", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
+        const int head_dim = (int)j.get("head_dim").as_int();
+        const int rot = (int)j.get_int("rotary_dim", head_dim);
+        const double theta = j.get("theta").as_double(), factor = j.get("factor").as_double();
+        const double low = j.get("low").as_double(), high = j.get("high").as_double(), original = j.get("original").as_double();
+        if (rot % 2 || rot <= 0 || rot > head_dim)
+            fail(KIPP_E_CONFIG, format("rotary_dim %d must be even, positive and at most head_dim %d", rot, head_dim));
+        if (!(theta > 0) || !(factor > 0) || !(low > 0) || !(high > low) || !(original > 0))
+            fail(KIPP_E_CONFIG, "stretched_rotary: theta, factor, low and original must be positive and high above low");
+        return std::make_unique<FrequencyTable>(stretched_frequencies(rot, theta, factor, low, high, original),
+                                                format("stretched/%.17g/%d/%.17g/%.17g/%.17g/%.17g", theta, rot, factor, low, high, original));
+    });
+    r.add_part_kind("dense_mlp", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
+        return std::make_unique<DenseFeedForward>((int)j.get("hidden_size").as_int(), (int)j.get("intermediate_size").as_int(),
+                                                  j.get_string("activation", "relu_squared"),
+                                                  tensor_names(j, {{"up", "up"}, {"down", "down"}}));
+    });
+    r.add_part_kind("parallel_block", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        const Registry& reg = Registry::get();
+        std::vector<std::string> names;
+        for (auto& n : j.get("names").items()) names.push_back(n.as_string());
+        const Json* ff = j.find("ffn");
+        return std::make_unique<ParallelBlock>(reg.make_as<Norm>(j.get("norm"), ctx, "a norm"),
+                                               reg.make_as<Mixer>(j.get("mixer"), ctx, "a mixer"),
+                                               ff && !ff->is_null() ? reg.make_as<FeedForward>(*ff, ctx, "a feed-forward") : nullptr,
+                                               names);
     });
     r.add_part_kind("rotary", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         const int head_dim = (int)j.get("head_dim").as_int();
@@ -861,6 +1118,11 @@ inline void register_builtin_parts() {
         options.keep_first = (int)j.get_int("keep_first", 0);
         options.head_mix = j.get_bool("head_mix", false);
         options.output_scale = j.get_double("output_scale", 1.0);
+        options.bias = j.get_bool("bias", false);
+        options.score_maps = (int)j.get_int("score_maps", 1);
+        options.combine_maps = j.get_bool("combine_maps", false);
+        options.lambda_init = j.get_double("lambda_init", 0.0);
+        options.combine_eps = j.get_double("combine_eps", 1e-5);
         options.names = tensor_names(j, options.names);
         return std::make_unique<AttentionMixer>(
             (int)j.get("hidden_size").as_int(), (int)j.get("num_heads").as_int(), (int)j.get("num_kv_heads").as_int(),
@@ -885,6 +1147,7 @@ inline void register_builtin_parts() {
             has_ffn ? reg.make_as<FeedForward>(*ff, ctx, "a feed-forward") : nullptr, names);
     });
     register_recurrent_parts(r);
+    register_latent_parts(r);
     r.add_part_kind("external", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
         const std::string role = j.get("role").as_string();
         if (role == "mixer") return std::make_unique<ExternalMixer>(j, ctx);

@@ -227,10 +227,12 @@ inline Json plan(const Json& c) {
 }  // namespace qwen3
 
 void register_venizen();                 // venizen.hpp
+void register_varunex();                 // varunex.hpp
 
 inline void register_builtin_architectures() {
     Registry::get().add_architecture("Qwen3ForCausalLM", Architecture{qwen3::normalize, qwen3::plan});
     register_venizen();
+    register_varunex();
 }
 
 }  // namespace kipp

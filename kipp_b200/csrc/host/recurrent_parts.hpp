@@ -3,6 +3,8 @@
 //
 //   retention     linear attention with one fixed decay per head, no softmax and no denominator
 //   delta_rule    the generalized delta rule: decay and removal rate per head, key channel and token
+//   gated_memory  the matrix memory of the xLSTM: exponential input and forget gates per head and
+//                 token, held stable by a running maximum, with a normalizer vector beside the matrix
 //   parallel      the sum of several mixers that read the same input
 //   polynorm_mlp  W_down act(W_up h), act = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3
 //
@@ -251,6 +253,116 @@ private:
 };
 
 // ---------------------------------------------------------------------------------------------
+// Gated matrix memory.  q = W_q h * query_scale (default dim^-1/2), k = W_k h [heads, dim],
+// v = W_v h [heads, value_dim]; per head a log input gate i = cap tanh((W_i h + b_i) / cap) and a
+// log forget gate f = logsigmoid(cap tanh((W_f h + b_f) / cap)).  With a running maximum m (0 at
+// the start): m_t = max(f_t + m_{t-1}, i_t), S_t = e^(f_t + m_{t-1} - m_t) S_{t-1} + e^(i_t - m_t) k_t v_t^T,
+// n_t the same with k_t alone, o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6).  Each head's o
+// divided by its root mean square (eps inside the root), heads concatenated, times the weight
+// `norm`, times gate(W_g h), times output_scale, through W_o.  S, n and m are float32 per request.
+class GatedMemoryMixer : public Mixer {
+public:
+    GatedMemoryMixer(const Json& j, const BuildContext&) {
+        hidden_ = (int)j.get("hidden_size").as_int();
+        heads_ = (int)j.get("num_heads").as_int();
+        dim_ = (int)j.get("head_dim").as_int();
+        v_dim_ = (int)j.get_int("value_dim", dim_);
+        cap_ = (float)j.get("gate_cap").as_double();
+        eps_ = (float)j.get("eps").as_double();
+        out_scale_ = (float)j.get_double("output_scale", 1.0);
+        q_scale_ = (float)j.get_double("query_scale", 1.0 / std::sqrt((double)dim_));
+        gate_ = gate_code(j.get_string("gate", "sigmoid"));
+        names_ = tensor_names(j, {{"q", "q"}, {"k", "k"}, {"v", "v"}, {"g", "g"}, {"i", "i"}, {"i_bias", "i.b"},
+                                  {"f", "f"}, {"f_bias", "f.b"}, {"norm", "norm"}, {"o", "o"}});
+        if (hidden_ <= 0 || heads_ <= 0 || dim_ <= 0 || v_dim_ <= 0) fail(KIPP_E_CONFIG, "gated_memory: sizes must be positive");
+        if (!(cap_ > 0)) fail(KIPP_E_CONFIG, "gated_memory: gate_cap must be positive");
+        qk_ = heads_ * dim_;
+        vv_ = heads_ * v_dim_;
+        g_off_ = 2 * qk_ + vv_;
+        i_off_ = g_off_ + (gate_ ? vv_ : 0);
+        cols_ = i_off_ + 2 * heads_;
+        ld_ = (cols_ + 7) / 8 * 8;
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
+            TensorSpec s;
+            s.name = p + names_.at(role);
+            s.shape = std::move(shape);
+            s.init = init;
+            out.push_back(s);
+        };
+        add("q", {qk_, hidden_});
+        add("k", {qk_, hidden_});
+        add("v", {vv_, hidden_});
+        if (gate_) add("g", {vv_, hidden_});
+        add("i", {heads_, hidden_});
+        add("i_bias", {heads_});
+        add("f", {heads_, hidden_});
+        add("f_bias", {heads_});
+        add("norm", {vv_}, "near_one");
+        add("o", {hidden_, vv_});
+    }
+    std::optional<StateSpec> state_spec() const override {
+        return StateSpec{{Ops::gated_memory_state_floats(heads_, dim_, v_dim_)}, F32};
+    }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        // one matrix for q, k, v, the output gate and the two gates of the memory
+        w_in_ = b.allocate((size_t)cols_ * hidden_ * es, p + "qkvgif");
+        char* base = static_cast<char*>(w_in_);
+        int row = 0;
+        auto put = [&](const char* role, int rows) {
+            b.load(p + names_.at(role), base + (size_t)row * hidden_ * es, dtype_, hidden_, rows, hidden_);
+            row += rows;
+        };
+        put("q", qk_);
+        put("k", qk_);
+        put("v", vv_);
+        if (gate_) put("g", vv_);
+        put("i", heads_);
+        put("f", heads_);
+        w_o_ = b.allocate((size_t)hidden_ * vv_ * es, p + names_.at("o"));
+        b.load(p + names_.at("o"), w_o_, dtype_, vv_, hidden_, vv_);
+        i_bias_ = load_f32(b, p + names_.at("i_bias"), heads_);
+        f_bias_ = load_f32(b, p + names_.at("f_bias"), heads_);
+        norm_ = load_f32(b, p + names_.at("norm"), vv_);
+        if (!Ops::gated_memory_ok(dim_, v_dim_))
+            fail(KIPP_E_UNSUPPORTED, format("gated_memory: the scan kernel does not take heads of %d x %d", dim_, v_dim_));
+    }
+    size_t weight_bytes() const override {
+        return ((size_t)cols_ + vv_) * hidden_ * dtype_size(dtype_) + ((size_t)2 * heads_ + vv_) * 4;
+    }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_in_, hidden_, w_in_, hidden_); }
+    void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        const size_t es = ctx.element();
+        Ops& ops = *ctx.ops;
+        const StepMeta& m = *ctx.meta;
+        NormFold fold_in, fold_out;
+        void* proj = ctx.workspace->buffer("memory_proj", (size_t)T * ld_ * es);
+        ops.gemm(proj, ctx.dtype, ld_, h, hidden_, w_in_, hidden_, dtype_, T, cols_, hidden_, EPI_STORE,
+                 fold_input(ctx, fold_in));
+        float* state = static_cast<float*>(ctx.state_view(run, mixer_slot, nullptr));
+        void* gated = ctx.workspace->buffer("memory_out", (size_t)T * vv_ * es);
+        ops.gated_memory_scan(gated, vv_, proj, ld_, ctx.dtype, 0, qk_, 2 * qk_, g_off_, i_off_, i_off_ + heads_, i_bias_,
+                              f_bias_, norm_, state, m.q_start, m.slots, m.shape.entries, T, heads_, dim_, v_dim_, cap_,
+                              q_scale_, eps_, out_scale_, gate_);
+        const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
+        ops.gemm(residual, F32, hidden_, gated, vv_, w_o_, vv_, dtype_, T, hidden_, vv_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
+    }
+
+private:
+    int hidden_ = 0, heads_ = 0, dim_ = 0, v_dim_ = 0, qk_ = 0, vv_ = 0, cols_ = 0, ld_ = 0, g_off_ = 0, i_off_ = 0;
+    int gate_ = 2, dtype_ = BF16;
+    float cap_ = 0.f, eps_ = 0.f, out_scale_ = 1.f, q_scale_ = 1.f;
+    std::map<std::string, std::string> names_;
+    void *w_in_ = nullptr, *w_o_ = nullptr;
+    float *i_bias_ = nullptr, *f_bias_ = nullptr, *norm_ = nullptr;
+};
+
+// ---------------------------------------------------------------------------------------------
 // Several mixers side by side: each reads the same input and adds its (scaled) output to the
 // residual stream; each has its own cache or state (mixer slot = its index).  The scale of a
 // branch is that mixer's own output_scale.
@@ -368,6 +480,9 @@ inline void register_recurrent_parts(Registry& r) {
     });
     r.add_part_kind("delta_rule", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
         return std::make_unique<DeltaRuleMixer>(j, ctx);
+    });
+    r.add_part_kind("gated_memory", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        return std::make_unique<GatedMemoryMixer>(j, ctx);
     });
     r.add_part_kind("parallel", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
         return std::make_unique<ParallelMixer>(j, ctx);

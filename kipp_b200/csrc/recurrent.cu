@@ -4,6 +4,9 @@
 //   retention        S_t = decay_h S_{t-1} + k_t v_t^T                      o_t = S_t^T q_t
 //   delta rule       S_t = diag(w_t) S_{t-1} - (a_t * u_t)(u_t^T S_{t-1}) + k_t v_t^T
 //                                                                           o_t = S_t^T r_t
+//   gated memory     m_t = max(f_t + m_{t-1}, i_t)   (m_0 = 0)
+//                    S_t = e^(f_t + m_{t-1} - m_t) S_{t-1} + e^(i_t - m_t) k_t v_t^T,  n_t likewise with k_t alone
+//                                        o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
 //
 // S is [key dim, value dim].  Retention rotates q and k by the step's (cos, sin)
 // table (pair (i, i + rot/2), the first `rot` dims) and scales k afterwards; its
@@ -14,6 +17,13 @@
 // square (eps inside the root), optionally multiplied by a weight, gated by
 // silu or sigmoid of a projection, scaled by out_scale and stored in the compute
 // type for the output projection.
+//
+// The gated memory (the matrix memory of the xLSTM) has a log input gate i = cap tanh((x_i + b_i) / cap)
+// and a log forget gate f = logsigmoid(cap tanh((x_f + b_f) / cap)) per head and token, q scaled by
+// q_scale.  Its n is carried as one more value column of S whose value is 1 in every token, so that
+// n_t . q_t is that column's output; the running maximum m is kept per head beside S (one copy per
+// slice of value columns, so that the blocks of a head do not share a word).  The state of a slot is
+// [heads][dim][v_dim + 4] (columns v_dim + 1 .. v_dim + 3 stay zero) followed by [heads][slices] of m.
 //
 // Everything that enters the recurrence is formed in float32 from the
 // projections (which arrive in the compute type); the state never leaves float32.
@@ -50,28 +60,55 @@ struct ScanArgs {
     int heads, dim, v_dim, batch;
     float k_scale, eps, out_scale;
     int gate;                              // 0 none, 1 silu, 2 sigmoid
+    // gated memory: columns of the two gates in proj, their biases [heads], the cap, the scale of q
+    int i_off, f_off;
+    const float* i_bias; const float* f_bias;
+    float gate_cap, q_scale;
+    long long slot_stride;                 // floats per slot of `state` (0: heads * dim * v_dim)
 };
+enum { RETENTION = 0, DELTA_RULE = 1, GATED_MEMORY = 2 };
+// vectors per token besides v, extra floats after them, extra value columns
+template <int KIND> struct Rec {
+    static constexpr int NV = KIND == DELTA_RULE ? 5 : 2;
+    static constexpr int XG = KIND == GATED_MEMORY ? 4 : 0;     // (i, f, 0, 0) after the vectors
+    static constexpr int XV = KIND == GATED_MEMORY ? 4 : 0;     // value columns (1, 0, 0, 0) after v
+};
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
 // (1) the token vectors: one record of NV * D + V floats per (head, token), heads outermost so that
 // a head's consecutive tokens are neighbours: NV = 5 (delta: r, k, w, a*u, u) or 2 (q, k), then v
-template <typename T, bool DELTA>
+template <typename T, int KIND>
 __global__ void __launch_bounds__(128)
 recurrent_prepare_kernel(const ScanArgs a, float* __restrict__ vec, int tokens) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int NV = DELTA ? 5 : 2;
+    constexpr bool DELTA = KIND == DELTA_RULE;
+    constexpr int NV = Rec<KIND>::NV, XG = Rec<KIND>::XG, XV = Rec<KIND>::XV;
     const int lane = threadIdx.x & 31;
     const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (wg >= (long long)tokens * a.heads) return;
     const size_t row = (size_t)(wg / a.heads);
     const int h = (int)(wg % a.heads), D = a.dim;
     const T* pr = static_cast<const T*>(a.proj) + row * a.ld_proj;
-    const int rec = NV * D + a.v_dim;
+    const int rec = NV * D + XG + a.v_dim + XV;
     float* dst = vec + ((size_t)h * tokens + row) * rec;
-    for (int c = lane; c < a.v_dim; c += 32) dst[NV * D + c] = to_f32(pr[a.v_off + h * a.v_dim + c]);
-    if (DELTA) {
+    for (int c = lane; c < a.v_dim; c += 32) dst[NV * D + XG + c] = to_f32(pr[a.v_off + h * a.v_dim + c]);
+    if (KIND == GATED_MEMORY) {
+        if (lane < XV) dst[NV * D + XG + a.v_dim + lane] = lane == 0 ? 1.f : 0.f;
+        if (lane == 0) {
+            const float cap = a.gate_cap;
+            dst[NV * D] = cap * tanhf((to_f32(pr[a.i_off + h]) + a.i_bias[h]) / cap);
+            dst[NV * D + 1] = log_sigmoid(cap * tanhf((to_f32(pr[a.f_off + h]) + a.f_bias[h]) / cap));
+            dst[NV * D + 2] = 0.f;
+            dst[NV * D + 3] = 0.f;
+        }
+        for (int d = lane; d < D; d += 32) {
+            dst[d] = to_f32(pr[a.q_off + h * D + d]) * a.q_scale;
+            dst[D + d] = to_f32(pr[a.k_off + h * D + d]);
+        }
+    } else if (DELTA) {
         const T* w_raw = static_cast<const T*>(a.w_raw);
         float ss = 0.f;
         for (int d = lane; d < D; d += 32) {
@@ -116,7 +153,6 @@ recurrent_prepare_kernel(const ScanArgs a, float* __restrict__ vec, int tokens) 
 // (2) the recurrence; raw o goes to o_raw [T, heads * v_dim] float32.  The records of a batch of
 // tokens come into shared memory by asynchronous copies, the next batch while this one is walked.
 constexpr int VS = 32;                     // value columns per block
-template <bool DELTA>
 __device__ __forceinline__ void load_batch(float* __restrict__ tv, float* __restrict__ vv, const float* __restrict__ rec0,
                                            int rec, int nvd, int nb, int slice, int V, bool async, int threads) {
     // rec0: the record of the batch's first token; the vectors' part [nvd] and this slice's values
@@ -141,14 +177,16 @@ __device__ __forceinline__ void load_batch(float* __restrict__ tv, float* __rest
     cp_async_commit();
 }
 
-template <typename T, bool DELTA, int P, int CHUNK>
+template <typename T, int KIND, int P, int CHUNK>
 __global__ void __launch_bounds__(VS * P)
 recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __restrict__ o_raw, int v_slices,
                       int tokens) {
     extern __shared__ __align__(16) float smem[];
-    constexpr int NV = DELTA ? 5 : 2;
-    const int D = a.dim, V = a.v_dim, TB = a.batch;
-    const int nvd = NV * D, rec = nvd + V;
+    constexpr bool DELTA = KIND == DELTA_RULE;
+    constexpr int NV = Rec<KIND>::NV;
+    // V counts the value columns of the state: those of v and, for the gated memory, n's and its padding
+    const int D = a.dim, V = a.v_dim + Rec<KIND>::XV, TB = a.batch;
+    const int nvd = NV * D + Rec<KIND>::XG, rec = nvd + V;
     // two buffers of [TB][NV][D] vectors followed by [TB][VS] values; their addresses are formed
     // from the shared base each time (a table of pointers would turn the loads into generic ones)
     const int buf_floats = TB * (nvd + VS);
@@ -161,7 +199,11 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     const int p = tid % P, cl = tid / P, col = slice * VS + cl;
     const int d0 = p * CHUNK;
     const bool live = col < V;
-    float* S_slot = a.state + ((size_t)a.slots[e] * a.heads + h) * (size_t)D * V;
+    float* slot_base = a.state + (size_t)a.slots[e] * (size_t)(a.slot_stride > 0 ? a.slot_stride : (long long)a.heads * D * V);
+    float* S_slot = slot_base + (size_t)h * D * V;
+    // the gated memory's running maximum: this block's own copy
+    float* m_slot = slot_base + (size_t)a.heads * D * V + (size_t)h * v_slices + slice;
+    float m_run = KIND == GATED_MEMORY ? *m_slot : 0.f;
     const float* recs = vec + ((size_t)h * tokens + row0) * rec;
     // 16-byte copies need every record and every part of it on a 16-byte boundary
     const bool async = nvd % 4 == 0 && V % 4 == 0;
@@ -171,12 +213,12 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     for (int i = 0; i < CHUNK; ++i) S[i] = (live && d0 + i < D) ? S_slot[(size_t)(d0 + i) * V + col] : 0.f;
     const float decay = DELTA ? 0.f : a.decay[h];
 
-    load_batch<DELTA>(smem, smem + TB * nvd, recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
+    load_batch(smem, smem + TB * nvd, recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
     int buf = 0;
     for (int t0 = 0; t0 < n_tok; t0 += TB, buf ^= 1) {
         const int nb = min(TB, n_tok - t0);
         if (t0 + TB < n_tok)
-            load_batch<DELTA>(smem + (buf ^ 1) * buf_floats, smem + (buf ^ 1) * buf_floats + TB * nvd,
+            load_batch(smem + (buf ^ 1) * buf_floats, smem + (buf ^ 1) * buf_floats + TB * nvd,
                               recs + (size_t)(t0 + TB) * rec, rec, nvd, min(TB, n_tok - t0 - TB), slice, V, async, VS * P);
         else
             cp_async_commit();
@@ -187,7 +229,14 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
         for (int tt = 0; tt < nb; ++tt) {
             const float v = vvb[tt * VS + cl];
             const float* base = tvb + tt * nvd + d0;
-            float us = 0.f;
+            float us = 0.f, keep = 0.f, take = 0.f;
+            if (KIND == GATED_MEMORY) {
+                const float gi = tvb[tt * nvd + NV * D], gf = tvb[tt * nvd + NV * D + 1];
+                const float m_new = fmaxf(gf + m_run, gi);
+                keep = expf(gf + m_run - m_new);
+                take = expf(gi - m_new);
+                m_run = m_new;
+            }
             if (DELTA) {
 #pragma unroll
                 for (int i = 0; i < CHUNK; ++i)
@@ -201,6 +250,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                 if (d0 + i < D) {
                     float s;
                     if (DELTA) s = fmaf(base[D + i], v, fmaf(-base[3 * D + i], us, base[2 * D + i] * S[i]));
+                    else if (KIND == GATED_MEMORY) s = fmaf(take * base[D + i], v, keep * S[i]);
                     else s = fmaf(base[D + i], v, decay * S[i]);
                     S[i] = s;
                     o = fmaf(s, base[i], o);
@@ -208,6 +258,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
             }
 #pragma unroll
             for (int x = P / 2; x > 0; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            if (KIND == GATED_MEMORY && col == a.v_dim + 1) o = m_run;      // the column after n's carries m_t to the finish
             if (live && p == 0) o_raw[(size_t)(row0 + t0 + tt) * (a.heads * V) + h * V + col] = o;
         }
         __syncthreads();                    // the buffer is free for the batch after the next
@@ -215,10 +266,11 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i)
         if (live && d0 + i < D) S_slot[(size_t)(d0 + i) * V + col] = S[i];
+    if (KIND == GATED_MEMORY && tid == 0) *m_slot = m_run;
 }
 
 // (3) per-head root-mean-square division, weight, gate, scale
-template <typename T>
+template <typename T, int KIND>
 __global__ void __launch_bounds__(128)
 recurrent_finish_kernel(const ScanArgs a, const float* __restrict__ o_raw, int tokens) {
     pdl_launch_dependents();
@@ -228,16 +280,22 @@ recurrent_finish_kernel(const ScanArgs a, const float* __restrict__ o_raw, int t
     if (wg >= (long long)tokens * a.heads) return;
     const size_t row = (size_t)(wg / a.heads);
     const int h = (int)(wg % a.heads), V = a.v_dim;
-    const float* o = o_raw + row * (a.heads * V) + h * V;
+    const int VX = V + Rec<KIND>::XV;
+    const float* o = o_raw + row * (a.heads * VX) + h * VX;
     const T* proj = static_cast<const T*>(a.proj);
     T* out = static_cast<T*>(a.out);
+    // the gated memory divides by max(|n . q|, e^(-m)) + 1e-6 first
+    const float den = KIND == GATED_MEMORY ? 1.0f / (fmaxf(fabsf(o[V]), expf(-o[V + 1])) + 1e-6f) : 1.f;
     float ss = 0.f;
-    for (int c = lane; c < V; c += 32) ss = fmaf(o[c], o[c], ss);
+    for (int c = lane; c < V; c += 32) {
+        const float y = o[c] * den;
+        ss = fmaf(y, y, ss);
+    }
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)V + a.eps);
     for (int c = lane; c < V; c += 32) {
         const int hc = h * V + c;
-        float y = o[c] * inv;
+        float y = o[c] * den * inv;
         if (a.norm_w != nullptr) y *= a.norm_w[hc];
         if (a.gate != 0) {
             const float g = to_f32(proj[row * a.ld_proj + a.g_off + hc]);
@@ -247,7 +305,7 @@ recurrent_finish_kernel(const ScanArgs a, const float* __restrict__ o_raw, int t
     }
 }
 
-template <typename T, bool DELTA, int P>
+template <typename T, int DELTA, int P>
 int launch_scan_chunk(const ScanArgs& b, const float* vec, float* o_raw, int slices, int tokens, dim3 grid, size_t smem,
                       cudaStream_t stream) {
     const int chunk = (b.dim + P - 1) / P;
@@ -258,22 +316,22 @@ int launch_scan_chunk(const ScanArgs& b, const float* vec, float* o_raw, int sli
 }
 
 // scratch: float32 [heads][tokens][NV * dim + v_dim] for the records, then [tokens][heads * v_dim] for raw o
-template <typename T, bool DELTA>
+template <typename T, int DELTA>
 int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cudaStream_t stream) {
-    const int D = a.dim, V = a.v_dim;
-    constexpr int NV = DELTA ? 5 : 2;
+    const int D = a.dim, V = a.v_dim + Rec<DELTA>::XV;
+    constexpr int NV = Rec<DELTA>::NV, XG = Rec<DELTA>::XG;
     // threads per column: runs of 8 key rows where the head allows (short chains of dependent
     // multiply-adds, more warps per block), at most 8 threads
     int P = 1;
     while (P < 8 && (D + P - 1) / P > 8) P *= 2;
     if ((D + P - 1) / P > MAX_CHUNK || scratch == nullptr) return KIPP_ERR_ARG;
-    const size_t per_token = ((size_t)NV * D + VS) * sizeof(float);
+    const size_t per_token = ((size_t)NV * D + XG + VS) * sizeof(float);
     int batch = (int)std::min<size_t>(32, (20 * 1024) / per_token);       // two buffers of at most 20 KB
     if (batch < 1) return KIPP_ERR_ARG;
     ScanArgs b = a;
     b.batch = batch;
     float* vec = scratch;
-    float* o_raw = scratch + (size_t)tokens * a.heads * (NV * D + V);
+    float* o_raw = scratch + (size_t)tokens * a.heads * (NV * D + XG + V);
     const long long warps = (long long)tokens * a.heads;
     const dim3 wgrid((unsigned)((warps + 3) / 4));
     int rc = kipp_launch(recurrent_prepare_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens);
@@ -288,7 +346,7 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     default: rc = launch_scan_chunk<T, DELTA, 8>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
     }
     if (rc) return rc;
-    return kipp_launch(recurrent_finish_kernel<T>, wgrid, dim3(128), 0, stream, 1, b, (const float*)o_raw, tokens);
+    return kipp_launch(recurrent_finish_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, (const float*)o_raw, tokens);
 }
 
 template <typename T>
@@ -304,13 +362,19 @@ __global__ void tanh_rows_kernel(T* __restrict__ out, long long ld_out, const T*
 }  // namespace
 
 // Whether the scan kernels take a head of these sizes.
-extern "C" int kipp_recurrent_scan_ok(int dim, int v_dim, int delta) {
-    if (dim <= 0 || v_dim <= 0 || dim > 8 * MAX_CHUNK) return 0;
-    return (((delta ? 5 : 2) * (size_t)dim + VS) * sizeof(float)) <= 20 * 1024 ? 1 : 0;
+extern "C" int kipp_recurrent_scan_ok(int dim, int v_dim, int kind) {
+    if (dim <= 0 || v_dim <= 0 || dim > 8 * MAX_CHUNK || kind < 0 || kind > 2) return 0;
+    return (((kind == DELTA_RULE ? 5 : 2) * (size_t)dim + 4 + VS) * sizeof(float)) <= 20 * 1024 ? 1 : 0;
 }
 // float32 values of scratch a scan of `tokens` tokens needs.
-extern "C" long long kipp_recurrent_scratch_floats(int tokens, int heads, int dim, int v_dim, int delta) {
-    return (long long)tokens * heads * ((delta ? 5 : 2) * (long long)dim + 2 * (long long)v_dim);
+extern "C" long long kipp_recurrent_scratch_floats(int tokens, int heads, int dim, int v_dim, int kind) {
+    const long long x = kind == GATED_MEMORY ? 4 : 0;
+    return (long long)tokens * heads * ((kind == DELTA_RULE ? 5 : 2) * (long long)dim + x + 2 * ((long long)v_dim + x));
+}
+// float32 values of state one request slot of the gated memory holds: S with n's column and its
+// padding, then one running maximum per head and slice of value columns.
+extern "C" long long kipp_gated_memory_state_floats(int heads, int dim, int v_dim) {
+    return (long long)heads * dim * (v_dim + 4) + (long long)heads * ((v_dim + 4 + VS - 1) / VS);
 }
 
 extern "C" int kipp_retention_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype,
@@ -326,8 +390,8 @@ extern "C" int kipp_retention_scan(void* out, long long ld_out, const void* proj
     a.decay = decay; a.cos_sin = rot > 0 ? cos_sin : nullptr; a.rot = rot; a.state = state;
     a.q_start = q_start; a.slots = slots; a.heads = heads; a.dim = dim; a.v_dim = v_dim;
     a.k_scale = k_scale; a.eps = eps; a.out_scale = out_scale; a.gate = gate;
-    if (dtype == KIPP_DT_F32) return launch_scan<float, false>(a, entries, tokens, scratch, (cudaStream_t)stream);
-    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, false>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_F32) return launch_scan<float, RETENTION>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, RETENTION>(a, entries, tokens, scratch, (cudaStream_t)stream);
     return KIPP_ERR_DTYPE;
 }
 
@@ -346,8 +410,33 @@ extern "C" int kipp_delta_rule_scan(void* out, long long ld_out, const void* pro
     a.w_raw = w_raw; a.ld_w = ld_w; a.a_bias = a_bias; a.w_bias = w_bias; a.norm_w = norm_w;
     a.state = state; a.q_start = q_start; a.slots = slots; a.heads = heads; a.dim = dim; a.v_dim = dim;
     a.k_scale = 1.f; a.eps = eps; a.out_scale = out_scale; a.gate = gate;
-    if (dtype == KIPP_DT_F32) return launch_scan<float, true>(a, entries, tokens, scratch, (cudaStream_t)stream);
-    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, true>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_F32) return launch_scan<float, DELTA_RULE>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, DELTA_RULE>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    return KIPP_ERR_DTYPE;
+}
+
+// The gated matrix memory (see the head of this file): q, k [heads, dim], v and the output gate
+// [heads, v_dim] and the two gates' pre-activations [heads] are columns of proj; the state of a slot
+// is kipp_gated_memory_state_floats floats.
+extern "C" int kipp_gated_memory_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype,
+                                      int q_off, int k_off, int v_off, int g_off, int i_off, int f_off,
+                                      const float* i_bias, const float* f_bias, const float* norm_w, float* state,
+                                      const int* q_start, const int* slots, int entries, int tokens, int heads,
+                                      int dim, int v_dim, float gate_cap, float q_scale, float eps, float out_scale,
+                                      int gate, float* scratch, void* stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
+    if (!kipp_recurrent_scan_ok(dim, v_dim, GATED_MEMORY) || heads <= 0 || i_bias == nullptr || f_bias == nullptr ||
+        !(gate_cap > 0.f))
+        return KIPP_ERR_ARG;
+    ScanArgs a = {};
+    a.out = out; a.ld_out = ld_out; a.proj = proj; a.ld_proj = ld_proj;
+    a.q_off = q_off; a.k_off = k_off; a.v_off = v_off; a.g_off = g_off; a.i_off = i_off; a.f_off = f_off;
+    a.i_bias = i_bias; a.f_bias = f_bias; a.norm_w = norm_w; a.gate_cap = gate_cap; a.q_scale = q_scale;
+    a.state = state; a.q_start = q_start; a.slots = slots; a.heads = heads; a.dim = dim; a.v_dim = v_dim;
+    a.k_scale = 1.f; a.eps = eps; a.out_scale = out_scale; a.gate = gate;
+    a.slot_stride = kipp_gated_memory_state_floats(heads, dim, v_dim);
+    if (dtype == KIPP_DT_F32) return launch_scan<float, GATED_MEMORY>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, GATED_MEMORY>(a, entries, tokens, scratch, (cudaStream_t)stream);
     return KIPP_ERR_DTYPE;
 }
 
