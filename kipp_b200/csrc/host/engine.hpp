@@ -1124,8 +1124,14 @@ inline void Engine::debug_part(const StepEntryView* entries, int n, int run_inde
         if (!pre) fail(KIPP_E_UNSUPPORTED, "this layer's block does not name its parts");
         return pre;
     };
+    ParallelBlock* shared_norm = dynamic_cast<ParallelBlock*>(block);
     if (which == "embedding") {
         for (auto& e : plan_->embedding) e.second->forward(ctx, residual);
+    } else if (which == "input_norm" && shared_norm != nullptr) {
+        shared_norm->norm()->forward(ctx, residual, output, nullptr, T);
+    } else if (which == "feed_forward" && shared_norm != nullptr) {
+        if (shared_norm->feed_forward() == nullptr) fail(KIPP_E_ARGUMENT, "the block has no feed-forward");
+        shared_norm->feed_forward()->forward(ctx, input, residual);
     } else if (which == "input_norm") {
         need_pre()->input_norm()->forward(ctx, residual, output, nullptr, T);
     } else if (which == "post_norm") {

@@ -775,6 +775,8 @@ public:
         if (ffn_) ffn_->forward(ctx, h, x);
         ctx.emitted = false;
     }
+    Norm* norm() { return norm_.get(); }
+    FeedForward* feed_forward() { return ffn_.get(); }
 
 private:
     std::unique_ptr<Norm> norm_;
