@@ -149,6 +149,26 @@ def venizen_of(size: str, vocab: int = 32000) -> dict:
             "layers": [par if i % 2 == 0 else delta for i in range(layers)], "loop": None}
 
 
+def varunex_of(size: str, vocab: int = 32000) -> dict:
+    """The design's three mixers in turn (gated matrix memory, attention over a cached latent,
+    differential attention with a window, the latent attention again), each beside a dense
+    feed-forward.  The differential layer's two maps have half a head each, the latent is four
+    heads wide and the rotated key part half a head, the memory's keys are half as wide as its values."""
+    width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
+    mlp = {"kind": "dense", "ff": ff}
+    memory = {"type": "mlstm", "mixer": {"heads": width // (2 * dim), "dim": dim, "vdim": 2 * dim, "gate_cap": 15.0}, "mlp": mlp}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": 4 * dim, "q_rank": width // 2,
+                        "rot": {"base": 1e6, "dims": dim // 2}, "scale": (dim + dim // 2) ** -0.5}, "mlp": mlp}
+    diff = {"type": "attention",
+            "mixer": {"heads": heads, "kv_heads": kv, "dim": dim // 2, "vdim": dim, "diff": 0.5, "mask": {"size": DESIGN_WINDOW},
+                      "rot": {"base": 5e4, "dims": dim // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}},
+                      "scale": (dim // 2) ** -0.5}, "mlp": mlp}
+    order = [memory, latent, diff, latent]
+    return {"architecture": "Varunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [order[i % 4] for i in range(layers)]}
+
+
 def qwen3_of(size: str, vocab: int = 32000) -> dict:
     width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
     return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=vocab, hidden_size=width,
@@ -159,22 +179,25 @@ def qwen3_of(size: str, vocab: int = 32000) -> dict:
 
 
 def compare_designs(args) -> int:
-    """Prefill and decode throughput of Venizen beside Qwen3 at equal layer sizes (random
-    weights), with the time of every kernel of a prompt step and of a decode step (an event
-    after every launch).  Prints ONE JSON line; the default workload's record is not touched."""
+    """Prefill and decode throughput of a design (--design-family) beside Qwen3 at equal layer
+    sizes (random weights), with the time of every kernel of a prompt step and of a decode step (an
+    event after every launch).  Prints ONE JSON line; the default workload's record is not touched."""
     import torch
     from kipp_b200.config import config_from_dict
     from kipp_b200.engine import Engine, StepEntry
     pk, pk_src = peaks()
     T, B, ctx = args.designs_prompt, args.batch, args.designs_prompt
-    out = {"metric": "prefill and decode tokens/s, Venizen beside Qwen3 at equal layer sizes", "dtype": "bf16",
+    families = {"venizen": [("venizen", venizen_of)], "varunex": [("varunex", varunex_of), ("venizen", venizen_of)]}
+    designs = families[args.design_family] + [("qwen3", qwen3_of)]
+    out = {"metric": "prefill and decode tokens/s, " + " and ".join(d.capitalize() for d, _ in designs[:-1]) +
+                     " beside Qwen3 at equal layer sizes", "dtype": "bf16",
            "data": "synthetic: random weights, seeded random token ids", "prompt_tokens": T, "decode_batch": B,
            "decode_context": ctx, "window": DESIGN_WINDOW, "peaks": pk, "peak_source": pk_src, "sizes": {}}
     g = torch.Generator().manual_seed(99)
     for size in args.designs.split(","):
         row = {}
-        for design, cfg in (("venizen", venizen_of(size)), ("qwen3", qwen3_of(size))):
-            config = config_from_dict(cfg)
+        for design, make in designs:
+            config = config_from_dict(make(size))
             eng = Engine.from_config(config, 7, dtype="bfloat16", page_size=PAGE, cache_tokens=(B + 1) * (ctx + 512),
                                      max_requests=B + 1, max_batch_tokens=max(T, B))
             stream, dev = eng.stream, eng.runtime.device
@@ -248,9 +271,11 @@ def main() -> int:
     ap.add_argument("--own-length-splits", action="store_true",
                     help="decode attention splits from each token's own context only")
     ap.add_argument("--designs", default=None, metavar="SIZES",
-                    help="instead of the default workload: the Venizen design beside Qwen3 at equal layer sizes, "
+                    help="instead of the default workload: a design (--design-family) beside Qwen3 at equal layer sizes, "
                          f"a list of {','.join(DESIGN_SIZES)} (prefill and decode tokens/s, time per kernel)")
     ap.add_argument("--designs-prompt", type=int, default=2048, help="prompt and decode context of --designs")
+    ap.add_argument("--design-family", default="venizen", choices=["venizen", "varunex"],
+                    help="the design --designs measures: venizen, or varunex (with Venizen, its closest relative, beside it)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

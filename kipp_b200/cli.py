@@ -25,7 +25,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="kipp", description="Qwen3 dense inference on one B200")
     ap.add_argument("--model", help="folder with config.json and *.safetensors")
     ap.add_argument("--random", metavar="PRESET|CONFIG.json",
-                    help="instead of --model: a preset name (tiny-a, tiny-b, venizen-tiny, qwen3-4b, qwen3-8b, qwen3-32b) or a "
+                    help="instead of --model: a preset name (tiny-a, tiny-b, venizen-tiny, varunex-tiny, qwen3-4b, qwen3-8b, qwen3-32b) or a "
                          "config.json, filled with random weights")
     ap.add_argument("--weights-seed", type=int, default=None,
                     help="seed of the random weights (default: the preset's, else 0)")
