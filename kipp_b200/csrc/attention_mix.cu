@@ -110,23 +110,27 @@ __device__ __forceinline__ float softmax_factor(float m, float l, const float* s
     return w / (l * w + expf(s - top));
 }
 
-// heads [n_q][v_dim] (float32, shared memory, already divided by their denominators) -> the
-// token's row of the output: the maps of a head combined, the gate, the scale.
+// heads [nh][v_dim] (float32, shared memory, already divided by their denominators): heads
+// h_first .. h_first + nh - 1 of the token -> their part of the token's row of the output: the maps
+// of a head combined (h_first and nh are even then), the gate, the scale.
 template <typename T>
 __device__ __forceinline__ void finish_heads(T* __restrict__ out, const float* __restrict__ heads, int t, int n_q,
-                                             int v_dim, float out_scale, const MixExtras& ex, int threads) {
+                                             int v_dim, float out_scale, const MixExtras& ex, int threads,
+                                             int h_first, int nh) {
     const T* gate = static_cast<const T*>(ex.gate);
     if (!ex.diff) {
-        for (int e = threadIdx.x; e < n_q * v_dim; e += threads) {
+        for (int e = threadIdx.x; e < nh * v_dim; e += threads) {
+            const int h = h_first + e / v_dim;
             float y = heads[e] * out_scale;
-            if (gate != nullptr) y *= sigmoid_(to_f32(gate[(size_t)t * ex.ld_gate + ex.gate_off + e / v_dim]));
-            out[(size_t)t * n_q * v_dim + e] = from_f32<T>(y);
+            if (gate != nullptr) y *= sigmoid_(to_f32(gate[(size_t)t * ex.ld_gate + ex.gate_off + h]));
+            out[((size_t)t * n_q + h_first) * v_dim + e] = from_f32<T>(y);
         }
         return;
     }
     const int lane = threadIdx.x & 31, n_out = n_q / 2;
-    for (int h = threadIdx.x >> 5; h < n_out; h += threads >> 5) {
-        const float* a1 = heads + (size_t)(2 * h) * v_dim;
+    for (int hl = threadIdx.x >> 5; hl < nh / 2; hl += threads >> 5) {
+        const int h = h_first / 2 + hl;
+        const float* a1 = heads + (size_t)(2 * hl) * v_dim;
         const float* a2 = a1 + v_dim;
         float ss = 0.f;
         for (int d = lane; d < v_dim; d += 32) {
@@ -326,39 +330,73 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
         acc[e] *= softmax_factor(m_run[h], l_run[h], ex.sink, h);
     }
     __syncthreads();
-    finish_heads(out, acc, t, n_q, v_dim, out_scale, ex, THREADS);
+    finish_heads(out, acc, t, n_q, v_dim, out_scale, ex, THREADS, 0, n_q);
 }
 
-// The runs of a token merged in run order: o = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M).
+// The runs of a token merged in run order: o = sum_r acc_r e^(m_r - M) / sum_r l_r e^(m_r - M).  A block
+// takes MERGE_HEADS heads of a token: a warp per head forms the runs' weights once, then every
+// thread sums its elements over the runs.
+constexpr int MERGE_HEADS = 2;
 template <typename T>
 __global__ void __launch_bounds__(THREADS)
 attention_mix_merge_kernel(T* __restrict__ out, const float* __restrict__ partial, const int* __restrict__ positions,
                            int n_q, int v_dim, int window, int keep_first, int max_runs, float out_scale,
                            const MixExtras ex) {
-    extern __shared__ __align__(16) float merged[];                 // [n_q][v_dim]
+    extern __shared__ __align__(16) float merged[];                 // [MERGE_HEADS][v_dim], weights [MERGE_HEADS][max_runs], factors
+    float* wts = merged + MERGE_HEADS * v_dim;
+    float* fac = wts + MERGE_HEADS * max_runs;
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, pos = positions[t];
+    const int t = blockIdx.x, pos = positions[t], h_first = blockIdx.y * MERGE_HEADS;
+    const int nh = min(MERGE_HEADS, n_q - h_first);
     int first, kept;
     visible_runs(pos, window, keep_first, first, kept);
     const int n_tiles = (kept + KT - 1) / KT + pos / KT - first / KT + 1;
     const int runs = min(max_runs, (n_tiles + SPLIT_TILES - 1) / SPLIT_TILES);
     const float* src = partial + (size_t)t * max_runs * n_q * (v_dim + 2);
-    for (int e = threadIdx.x; e < n_q * v_dim; e += THREADS) {
-        const int h = e / v_dim, d = e % v_dim;
+    const int lane = threadIdx.x & 31;
+    for (int hl = threadIdx.x >> 5; hl < nh; hl += THREADS / 32) {
+        const int h = h_first + hl;
         float m = -INFINITY;
-        for (int r = 0; r < runs; ++r) m = fmaxf(m, src[((size_t)r * n_q + h) * (v_dim + 2)]);
-        float l = 0.f, o = 0.f;
-        for (int r = 0; r < runs; ++r) {
+        for (int r = lane; r < runs; r += 32) m = fmaxf(m, src[((size_t)r * n_q + h) * (v_dim + 2)]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int r = lane; r < runs; r += 32) {
             const float* p = src + ((size_t)r * n_q + h) * (v_dim + 2);
             const float w = p[0] == -INFINITY ? 0.f : expf(p[0] - m);
+            wts[hl * max_runs + r] = w;
             l = fmaf(p[1], w, l);
-            o = fmaf(p[2 + d], w, o);
         }
-        merged[e] = o * softmax_factor(m, l, ex.sink, h);
+        l = warp_sum(l);
+        if (lane == 0) fac[hl] = softmax_factor(m, l, ex.sink, h);
     }
     __syncthreads();
-    finish_heads(out, merged, t, n_q, v_dim, out_scale, ex, THREADS);
+    for (int e = threadIdx.x; e < nh * v_dim; e += THREADS) {
+        const int hl = e / v_dim, d = e % v_dim;
+        const float* p = src + (size_t)(h_first + hl) * (v_dim + 2) + 2 + d;
+        float o = 0.f;
+        for (int r = 0; r < runs; ++r) o = fmaf(p[(size_t)r * n_q * (v_dim + 2)], wts[hl * max_runs + r], o);
+        merged[e] = o * fac[hl];
+    }
+    __syncthreads();
+    finish_heads(out, merged, t, n_q, v_dim, out_scale, ex, THREADS, h_first, nh);
+}
+
+// Launches the merge of `runs` runs per token.
+template <typename T>
+int launch_merge(void* out, const float* partial, const int* positions, int tokens, int n_q, int v_dim, int window,
+                 int keep_first, int runs, float out_scale, const MixExtras& ex, cudaStream_t s) {
+    const size_t smem = ((size_t)MERGE_HEADS * (v_dim + runs + 1) + 3) * sizeof(float);
+    auto merge = attention_mix_merge_kernel<T>;
+    static size_t allowed = 0;
+    if (smem > 48 * 1024 && smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(merge, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+        allowed = smem;
+    }
+    const dim3 grid((unsigned)tokens, (unsigned)((n_q + MERGE_HEADS - 1) / MERGE_HEADS));
+    return kipp_launch(merge, grid, dim3(THREADS), smem, s, 1, (T*)out, partial, positions, n_q, v_dim, window, keep_first,
+                       runs, out_scale, ex);
 }
 
 template <typename T>
@@ -391,16 +429,7 @@ int launch_mix(void* out, const void* q, const void* k_pages, const void* v_page
                          block_table, table_width, page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
                          out_scale, split, partial, kv_stage, status, ex);
     if (rc || !split) return rc;
-    const size_t merge_smem = (size_t)n_q * v_dim * sizeof(float);
-    auto merge = attention_mix_merge_kernel<T>;
-    static size_t merge_allowed = 0;
-    if (merge_smem > 48 * 1024 && merge_smem > merge_allowed) {
-        cudaError_t e = cudaFuncSetAttribute(merge, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)merge_smem);
-        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
-        merge_allowed = merge_smem;
-    }
-    return kipp_launch(merge, dim3((unsigned)tokens), dim3(THREADS), merge_smem, s, 1, (T*)out,
-                       (const float*)partial, positions, n_q, v_dim, window, keep_first, runs, out_scale, ex);
+    return launch_merge<T>(out, partial, positions, tokens, n_q, v_dim, window, keep_first, runs, out_scale, ex, s);
 }
 
 // ---------------------------------------------------------------------------
@@ -414,6 +443,9 @@ int launch_mix(void* out, const void* q, const void* k_pages, const void* v_page
 // warp that owns the head.  The weights P keep float32 precision through the 16-bit product:
 // P = hi + lo with hi = bf16(P), lo = bf16(P - hi), two products into the same accumulator.
 // K and V tiles share one buffer: V is fetched (asynchronously) while the softmax runs.
+// Of the options of MixExtras it takes score maps (a key row holds the keys of a head's maps side by
+// side; with two maps a warp owns both maps of its heads, so that it combines them from its own
+// registers), the sink and the gate; not values that lie in their key rows.
 constexpr int QB = 8;
 constexpr int MMA_THREADS = 256;
 
@@ -426,9 +458,10 @@ __device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t 
 struct MmaSmem {
     int ldq, ldkv, lds, ldp;
     size_t qs, kv, phi, plo, sraw, mix, m_run, l_run, corr, pg, bytes;     // byte offsets
-    __host__ __device__ MmaSmem(int n_q, int n_kv, int head_dim, int v_dim) {
+    // k_row: elements of a key row (head_dim x score maps per head)
+    __host__ __device__ MmaSmem(int n_q, int n_kv, int head_dim, int v_dim, int k_row) {
         ldq = head_dim + 8;
-        ldkv = (head_dim > v_dim ? head_dim : v_dim) + 8;
+        ldkv = (k_row > v_dim ? k_row : v_dim) + 8;
         lds = KT + 1;
         ldp = KT + 8;
         size_t at = 0;
@@ -453,9 +486,13 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
                          const int* __restrict__ work, const int* __restrict__ q_start,
                          const int* __restrict__ context_len, const int* __restrict__ block_table, int table_width,
                          int page_size, int n_q, int n_kv, int head_dim, int v_dim, float scale, int window,
-                         int keep_first, float out_scale, int* __restrict__ status) {
+                         int keep_first, float out_scale, int* __restrict__ status, const MixExtras ex) {
     extern __shared__ __align__(16) unsigned char raw[];
-    const MmaSmem L(n_q, n_kv, head_dim, v_dim);
+    const int maps = ex.key_maps, k_row = maps * head_dim;
+    const MmaSmem L(n_q, n_kv, head_dim, v_dim, k_row);
+    // the heads a warp owns: warp, warp + 8, ...; with two maps per head both maps of heads warp, warp + 8, ...
+    const bool pairs = maps == 2;
+#define KIPP_OWNED_HEAD(hh) (pairs ? 2 * (warp + 8 * ((hh) >> 1)) + ((hh) & 1) : warp + 8 * (hh))
     bf16* qs = reinterpret_cast<bf16*>(raw + L.qs);
     bf16* kv = reinterpret_cast<bf16*>(raw + L.kv);
     bf16* phi = reinterpret_cast<bf16*>(raw + L.phi);
@@ -504,7 +541,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
     const int win0 = first_lo / KT;
     const int kept_only = min((kept_hi + KT - 1) / KT, win0);
     const int n_tiles = kept_only + pos_hi / KT - win0 + 1;
-    const int kchunks = head_dim / 8, vchunks = v_dim / 8;
+    const int kchunks = k_row / 8, vchunks = v_dim / 8;
     for (int it = 0; it < n_tiles; ++it) {
         const int j0 = it < kept_only ? it * KT : (win0 + it - kept_only) * KT;
         __syncthreads();                                            // the tile before is done with kv and P
@@ -523,7 +560,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         for (int rr = tid >> 3; rr < n_kv * KT; rr += MMA_THREADS / 8) {
             const int jj = rr & (KT - 1), g = rr / KT;
             const bool ok = pg[jj] >= 0;
-            const bf16* src = ok ? k_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * head_dim : k_pages;
+            const bf16* src = ok ? k_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * k_row : k_pages;
             const uint32_t dst = smem_address(kv + (size_t)rr * ldkv);
             for (int c = tid & 7; c < kchunks; c += 8) cp_async16(dst + c * 16, ok ? src + c * 8 : src, ok ? 16 : 0);
         }
@@ -533,9 +570,9 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         // ---- S^T = K Q^T for the heads this warp owns
 #pragma unroll
         for (int hh = 0; hh < HPW; ++hh) {
-            const int h = warp + 8 * hh;
+            const int h = KIPP_OWNED_HEAD(hh);
             if (h >= n_q) break;
-            const bf16* kg = kv + (size_t)(h / group) * KT * ldkv;
+            const bf16* kg = kv + (size_t)(h / group) * KT * ldkv + (h % maps) * head_dim;
             const bf16* qh = qs + (size_t)h * QB * ldq;
             float c[2][4];
 #pragma unroll
@@ -651,7 +688,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         // ---- O^T += V^T P^T for the heads this warp owns
 #pragma unroll
         for (int hh = 0; hh < HPW; ++hh) {
-            const int h = warp + 8 * hh;
+            const int h = KIPP_OWNED_HEAD(hh);
             if (h >= n_q) break;
             const bf16* vg = kv + (size_t)(h / group) * KT * ldkv;
             const float c0 = corr[h * QB + tig * 2], c1 = corr[h * QB + tig * 2 + 1];
@@ -684,12 +721,63 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         }
     }
     __syncthreads();
+    const bf16* gate = static_cast<const bf16*>(ex.gate);
+    if (ex.diff) {
+        // both maps of a head are this warp's: o = a1 - lambda a2 over the head's value dims, which lie
+        // in this thread (value blocks) and in the lanes of equal tig (gid), per query
+#pragma unroll
+        for (int hh = 0; hh + 1 < HPW; hh += 2) {
+            const int h = KIPP_OWNED_HEAD(hh);
+            if (h + 1 >= n_q) break;
+            float f1[2], f2[2], ss[2] = {0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                f1[c] = softmax_factor(m_run[h * QB + tig * 2 + c], l_run[h * QB + tig * 2 + c], ex.sink, h);
+                f2[c] = softmax_factor(m_run[(h + 1) * QB + tig * 2 + c], l_run[(h + 1) * QB + tig * 2 + c], ex.sink, h + 1);
+            }
+#pragma unroll
+            for (int vb = 0; vb < VB; ++vb) {
+                if (vb * 16 >= v_dim) break;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float d = fmaf(-ex.lambda, o[hh + 1][vb][i] * f2[i & 1], o[hh][vb][i] * f1[i & 1]);
+                    o[hh][vb][i] = d;
+                    ss[i & 1] = fmaf(d, d, ss[i & 1]);
+                }
+            }
+#pragma unroll
+            for (int x = 4; x < 32; x <<= 1) {
+                ss[0] += __shfl_xor_sync(0xffffffffu, ss[0], x);
+                ss[1] += __shfl_xor_sync(0xffffffffu, ss[1], x);
+            }
+            const int n_out = n_q / 2, ho = h / 2;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                if (tig * 2 + c >= n_tok) continue;
+                const int row = row0 + tig * 2 + c;
+                float f = ex.diff_scale * out_scale / sqrtf(ss[c] / (float)v_dim + ex.diff_eps);
+                if (gate != nullptr) f *= sigmoid_(to_f32(gate[(size_t)row * ex.ld_gate + ex.gate_off + ho]));
+                bf16* dst = out + ((size_t)row * n_out + ho) * v_dim;
+#pragma unroll
+                for (int vb = 0; vb < VB; ++vb) {
+                    if (vb * 16 >= v_dim) break;
+                    dst[vb * 16 + gid] = __float2bfloat16_rn(o[hh][vb][c] * f);
+                    dst[vb * 16 + gid + 8] = __float2bfloat16_rn(o[hh][vb][2 + c] * f);
+                }
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int hh = 0; hh < HPW; ++hh) {
-        const int h = warp + 8 * hh;
+        const int h = KIPP_OWNED_HEAD(hh);
         if (h >= n_q) break;
-        const float l0 = l_run[h * QB + tig * 2], l1 = l_run[h * QB + tig * 2 + 1];
-        const float i0 = l0 > 0.f ? out_scale / l0 : 0.f, i1 = l1 > 0.f ? out_scale / l1 : 0.f;
+        float i0 = softmax_factor(m_run[h * QB + tig * 2], l_run[h * QB + tig * 2], ex.sink, h) * out_scale;
+        float i1 = softmax_factor(m_run[h * QB + tig * 2 + 1], l_run[h * QB + tig * 2 + 1], ex.sink, h) * out_scale;
+        if (gate != nullptr) {
+            if (tig * 2 < n_tok) i0 *= sigmoid_(to_f32(gate[(size_t)(row0 + tig * 2) * ex.ld_gate + ex.gate_off + h]));
+            if (tig * 2 + 1 < n_tok) i1 *= sigmoid_(to_f32(gate[(size_t)(row0 + tig * 2 + 1) * ex.ld_gate + ex.gate_off + h]));
+        }
 #pragma unroll
         for (int vb = 0; vb < VB; ++vb) {
             if (vb * 16 >= v_dim) break;
@@ -706,6 +794,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
             }
         }
     }
+#undef KIPP_OWNED_HEAD
 }
 
 template <int HPW, int VB, typename... Args>
@@ -719,39 +808,350 @@ int launch_mix_mma(size_t smem, int items, cudaStream_t s, Args... args) {
     }
     return kipp_launch(kernel, dim3((unsigned)items), dim3(MMA_THREADS), smem, s, 1, args...);
 }
+
+// ---------------------------------------------------------------------------
+// One key row per token that all heads share and that also holds the value (values_in_keys with
+// one kv head: a latent), in bfloat16 on the tensor cores (mma.sync m16n8k16).  The heads need
+// nothing of one another here, so the 16 rows of the instruction's M are 16 HEADS of one token: a
+// block of 4 warps takes (token, group of 16 heads[, run of key tiles]).  Per tile of 32 keys:
+// S[16 heads][32 keys] = Q K^T (each warp 8 keys, head_dim as K), scores to shared memory in
+// float32, a softmax step per head row (lane = key), then O[16][v_dim] += P V with the value
+// columns dealt out to the warps (VB tiles of 8 columns each, accumulators in registers).  The
+// weights keep float32 precision through the 16-bit product (P = hi + lo, as above).  Tiles are
+// aligned to absolute positions and cut into the same runs as the CUDA-core kernel's, so the
+// same merge kernel finishes a step of few tokens; a prompt's tokens walk all their tiles and
+// finish (sink, gate, scale) from their registers.
+constexpr int SK_ROWS = 16, SK_THREADS = 128;
+
+struct SharedKeySmem {
+    int ldq, lds, ldp;
+    size_t qs, ks, phi, plo, sraw, m_run, l_run, corr, pg, bytes;
+    __host__ __device__ SharedKeySmem(int head_dim) {
+        ldq = head_dim + 8;
+        lds = KT + 1;
+        ldp = KT + 8;
+        size_t at = 0;
+        qs = at; at += (size_t)SK_ROWS * ldq * 2;
+        ks = at; at += (size_t)KT * ldq * 2;
+        phi = at; at += (size_t)SK_ROWS * ldp * 2;
+        plo = at; at += (size_t)SK_ROWS * ldp * 2;
+        sraw = at; at += (size_t)SK_ROWS * lds * 4;
+        m_run = at; at += SK_ROWS * 4;
+        l_run = at; at += SK_ROWS * 4;
+        corr = at; at += SK_ROWS * 4;
+        pg = at; at += 2 * KT * 4;
+        bytes = at;
+    }
+};
+
+template <int VB>
+__global__ void __launch_bounds__(SK_THREADS)
+attention_shared_key_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
+                            const int* __restrict__ positions, const int* __restrict__ entry_of_token,
+                            const int* __restrict__ block_table, int table_width, int page_size, int n_q,
+                            int head_dim, int v_dim, float scale, int window, float out_scale, int split,
+                            float* __restrict__ partial, int* __restrict__ status, const MixExtras ex) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    const SharedKeySmem L(head_dim);
+    bf16* qs = reinterpret_cast<bf16*>(raw + L.qs);
+    bf16* ks = reinterpret_cast<bf16*>(raw + L.ks);
+    bf16* phi = reinterpret_cast<bf16*>(raw + L.phi);
+    bf16* plo = reinterpret_cast<bf16*>(raw + L.plo);
+    float* sraw = reinterpret_cast<float*>(raw + L.sraw);
+    float* m_run = reinterpret_cast<float*>(raw + L.m_run);
+    float* l_run = reinterpret_cast<float*>(raw + L.l_run);
+    float* corr = reinterpret_cast<float*>(raw + L.corr);
+    int* pg = reinterpret_cast<int*>(raw + L.pg);
+    int* sl = pg + KT;
+    const int ldq = L.ldq, lds = L.lds, ldp = L.ldp;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int t = blockIdx.x, h0 = blockIdx.y * SK_ROWS;
+    const int pos = positions[t];
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int win0 = first / KT;
+    const int n_tiles = pos / KT - win0 + 1;
+    const int it0 = split ? blockIdx.z * SPLIT_TILES : 0;
+    if (it0 >= n_tiles) return;
+    const int it1 = split ? min(n_tiles, it0 + SPLIT_TILES) : n_tiles;
+    const int* table = block_table + (size_t)entry_of_token[t] * table_width;
+
+    const int chunks = head_dim / 8;
+    for (int i = tid; i < SK_ROWS * chunks; i += SK_THREADS) {
+        const int c = i % chunks, r = i / chunks;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (h0 + r < n_q) v = *reinterpret_cast<const uint4*>(q + ((size_t)t * n_q + h0 + r) * head_dim + c * 8);
+        *reinterpret_cast<uint4*>(qs + (size_t)r * ldq + c * 8) = v;
+    }
+    if (tid < SK_ROWS) { m_run[tid] = -INFINITY; l_run[tid] = 0.f; corr[tid] = 1.f; }
+    float o[VB][4];
+#pragma unroll
+    for (int b = 0; b < VB; ++b) o[b][0] = o[b][1] = o[b][2] = o[b][3] = 0.f;
+    const int col0 = warp * VB * 8;                                 // this warp's value columns
+
+    for (int it = it0; it < it1; ++it) {
+        const int j0 = (win0 + it) * KT;
+        __syncthreads();                                            // the tile before is done with K and P
+        if (tid < KT) {
+            const int j = j0 + tid;
+            int page = -1;
+            if (j >= first && j <= pos) {
+                page = j / page_size < table_width ? table[j / page_size] : -1;
+                if (page < 0) atomicExch(status, 3);
+            }
+            pg[tid] = page;
+            sl[tid] = j % page_size;
+        }
+        __syncthreads();
+        for (int rr = tid >> 2; rr < KT; rr += SK_THREADS / 4) {    // four threads per key row
+            const bool ok = pg[rr] >= 0;
+            const bf16* src = ok ? k_pages + ((size_t)pg[rr] * page_size + sl[rr]) * head_dim : k_pages;
+            const uint32_t dst = smem_address(ks + (size_t)rr * ldq);
+            for (int c = tid & 3; c < chunks; c += 4) cp_async16(dst + c * 16, ok ? src + c * 8 : src, ok ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+        // ---- S = Q K^T: this warp's 8 keys
+        {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const bf16* kr = ks + (size_t)(warp * 8 + gid) * ldq + tig * 2;
+            const bf16* qa = qs + (size_t)gid * ldq + tig * 2;
+            for (int k0 = 0; k0 < head_dim; k0 += 16) {
+                uint32_t a[4];
+                a[0] = *reinterpret_cast<const uint32_t*>(qa + k0);
+                a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * ldq + k0);
+                a[2] = *reinterpret_cast<const uint32_t*>(qa + k0 + 8);
+                a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * ldq + k0 + 8);
+                mma_16816(c, a, *reinterpret_cast<const uint32_t*>(kr + k0), *reinterpret_cast<const uint32_t*>(kr + k0 + 8));
+            }
+            const int key = warp * 8 + tig * 2;
+            sraw[gid * lds + key] = c[0] * scale;
+            sraw[gid * lds + key + 1] = c[1] * scale;
+            sraw[(gid + 8) * lds + key] = c[2] * scale;
+            sraw[(gid + 8) * lds + key + 1] = c[3] * scale;
+        }
+        __syncthreads();
+        // ---- a softmax step for four head rows per warp (lane = key)
+        {
+            const bool vis = pg[lane] >= 0;
+            float sv[4], mx[4], p[4], ps[4], m_old[4], cf[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = warp * 4 + i;
+                sv[i] = vis ? sraw[r * lds + lane] : -INFINITY;
+                m_old[i] = m_run[r];
+                mx[i] = sv[i];
+            }
+#pragma unroll
+            for (int x = 16; x > 0; x >>= 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], x));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                mx[i] = fmaxf(mx[i], m_old[i]);
+                p[i] = 0.f;
+                cf[i] = 1.f;
+                if (mx[i] != -INFINITY) {
+                    p[i] = sv[i] == -INFINITY ? 0.f : expf(sv[i] - mx[i]);
+                    cf[i] = m_old[i] == -INFINITY ? 0.f : expf(m_old[i] - mx[i]);
+                }
+                ps[i] = p[i];
+            }
+#pragma unroll
+            for (int x = 16; x > 0; x >>= 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ps[i] += __shfl_xor_sync(0xffffffffu, ps[i], x);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = warp * 4 + i;
+                const bf16 hi = __float2bfloat16_rn(p[i]);
+                phi[r * ldp + lane] = hi;
+                plo[r * ldp + lane] = __float2bfloat16_rn(p[i] - __bfloat162float(hi));
+                if (lane == 0) {
+                    l_run[r] = l_run[r] * cf[i] + ps[i];
+                    m_run[r] = mx[i];
+                    corr[r] = cf[i];
+                }
+            }
+        }
+        __syncthreads();
+        // ---- O += P V: the value of a key is the head of its row
+        {
+            const float c0 = corr[gid], c1 = corr[gid + 8];
+            uint32_t ah[2][4], al[2][4];
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2) {
+                const int at = gid * ldp + s2 * 16 + tig * 2;
+                ah[s2][0] = *reinterpret_cast<const uint32_t*>(phi + at);
+                ah[s2][1] = *reinterpret_cast<const uint32_t*>(phi + at + 8 * ldp);
+                ah[s2][2] = *reinterpret_cast<const uint32_t*>(phi + at + 8);
+                ah[s2][3] = *reinterpret_cast<const uint32_t*>(phi + at + 8 * ldp + 8);
+                al[s2][0] = *reinterpret_cast<const uint32_t*>(plo + at);
+                al[s2][1] = *reinterpret_cast<const uint32_t*>(plo + at + 8 * ldp);
+                al[s2][2] = *reinterpret_cast<const uint32_t*>(plo + at + 8);
+                al[s2][3] = *reinterpret_cast<const uint32_t*>(plo + at + 8 * ldp + 8);
+            }
+#pragma unroll
+            for (int b = 0; b < VB; ++b) {
+                const int col = col0 + b * 8;
+                if (col >= v_dim) break;
+                o[b][0] *= c0; o[b][1] *= c0; o[b][2] *= c1; o[b][3] *= c1;
+#pragma unroll
+                for (int s2 = 0; s2 < 2; ++s2) {
+                    const unsigned short* v0 = reinterpret_cast<const unsigned short*>(ks) + (size_t)(s2 * 16 + tig * 2) * ldq + col + gid;
+                    const uint32_t b0 = (uint32_t)v0[0] | ((uint32_t)v0[ldq] << 16);
+                    const uint32_t b1 = (uint32_t)v0[8 * ldq] | ((uint32_t)v0[9 * ldq] << 16);
+                    mma_16816(o[b], ah[s2], b0, b1);
+                    mma_16816(o[b], al[s2], b0, b1);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // rows gid and gid + 8 are heads h0 + gid and h0 + gid + 8; a thread holds columns col + 2 tig, + 1
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = gid + 8 * half, h = h0 + r;
+        if (h >= n_q) continue;
+        if (split) {
+            float* dst = partial + (((size_t)t * gridDim.z + blockIdx.z) * n_q + h) * (v_dim + 2);
+            if (warp == 0 && tig == 0) { dst[0] = m_run[r]; dst[1] = l_run[r]; }
+#pragma unroll
+            for (int b = 0; b < VB; ++b) {
+                const int col = col0 + b * 8 + tig * 2;
+                if (col0 + b * 8 >= v_dim) break;
+                dst[2 + col] = o[b][2 * half];
+                dst[2 + col + 1] = o[b][2 * half + 1];
+            }
+        } else {
+            float f = softmax_factor(m_run[r], l_run[r], ex.sink, h) * out_scale;
+            if (ex.gate != nullptr)
+                f *= sigmoid_(to_f32(static_cast<const bf16*>(ex.gate)[(size_t)t * ex.ld_gate + ex.gate_off + h]));
+            bf16* dst = out + ((size_t)t * n_q + h) * v_dim;
+#pragma unroll
+            for (int b = 0; b < VB; ++b) {
+                const int col = col0 + b * 8 + tig * 2;
+                if (col0 + b * 8 >= v_dim) break;
+                *reinterpret_cast<__nv_bfloat162*>(dst + col) = __floats2bfloat162_rn(o[b][2 * half] * f, o[b][2 * half + 1] * f);
+            }
+        }
+    }
+}
+
+template <int VB>
+int launch_shared_key(void* out, const void* q, const void* k_pages, const int* positions, const int* entry_of_token,
+                      const int* block_table, int table_width, int page_size, int tokens, int n_q, int head_dim,
+                      int v_dim, float scale, int window, float out_scale, int runs, float* partial, int* status,
+                      const MixExtras& ex, cudaStream_t s) {
+    const size_t smem = SharedKeySmem(head_dim).bytes;
+    auto kernel = attention_shared_key_kernel<VB>;
+    static size_t allowed = 0;
+    if (smem > 48 * 1024 && smem > allowed) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
+        allowed = smem;
+    }
+    const int split = runs > 1 ? 1 : 0;
+    const dim3 grid((unsigned)tokens, (unsigned)((n_q + SK_ROWS - 1) / SK_ROWS), (unsigned)(split ? runs : 1));
+    int rc = kipp_launch(kernel, grid, dim3(SK_THREADS), smem, s, 1, (bf16*)out, (const bf16*)q, (const bf16*)k_pages,
+                         positions, entry_of_token, block_table, table_width, page_size, n_q, head_dim, v_dim, scale,
+                         window, out_scale, split, partial, status, ex);
+    if (rc || !split) return rc;
+    return launch_merge<bf16>(out, partial, positions, tokens, n_q, v_dim, window, 0, runs, out_scale, ex, s);
+}
 }  // namespace
 
+// Whether the tensor-core kernel for one shared key row per token takes these sizes (bfloat16 only).
+extern "C" int kipp_attention_shared_key_ok(int n_q, int head_dim, int v_dim) {
+    if (n_q <= 0 || head_dim <= 0 || v_dim <= 0 || head_dim % 16 || v_dim % 8 || v_dim > head_dim || v_dim > 512) return 0;
+    return SharedKeySmem(head_dim).bytes <= 200 * 1024 ? 1 : 0;
+}
+
+// n_q heads over one key row of head_dim per token whose first v_dim elements are its value.
+// extras: sink and gate of MixExtras (values_in_keys is what this kernel is; no maps, no mix).
+extern "C" int kipp_attention_shared_key(void* out, const void* q, const void* k_pages, const int* positions,
+                                         const int* entry_of_token, const int* block_table, int table_width,
+                                         int page_size, int tokens, int n_q, int head_dim, int v_dim, float scale,
+                                         int window, float out_scale, int runs, float* partial, const void* extras,
+                                         int* status, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!kipp_attention_shared_key_ok(n_q, head_dim, v_dim) || page_size <= 0 || window < 0 || runs < 1 ||
+        (runs > 1 && partial == nullptr) || runs > 65535)
+        return KIPP_ERR_ARG;
+    if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)out) & 15) != 0) return -3;
+    MixExtras ex = {};
+    ex.key_maps = 1;
+    if (extras != nullptr) ex = *static_cast<const MixExtras*>(extras);
+    if (ex.key_maps != 1 || ex.diff) return KIPP_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int vb = (v_dim + 31) / 32;
+#define KIPP_SHARED_KEY(V)                                                                                            \
+    return launch_shared_key<V>(out, q, k_pages, positions, entry_of_token, block_table, table_width, page_size,      \
+                                tokens, n_q, head_dim, v_dim, scale, window, out_scale, runs, partial, status, ex, s)
+    if (vb <= 1) KIPP_SHARED_KEY(1);
+    if (vb <= 2) KIPP_SHARED_KEY(2);
+    if (vb <= 4) KIPP_SHARED_KEY(4);
+    if (vb <= 8) KIPP_SHARED_KEY(8);
+    KIPP_SHARED_KEY(16);
+#undef KIPP_SHARED_KEY
+}
+
 // Whether the tensor-core prompt kernel takes these sizes (bfloat16 only).
-extern "C" int kipp_attention_mix_mma_ok(int n_q, int n_kv, int head_dim, int v_dim) {
-    if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q > 32) return 0;
+extern "C" int kipp_attention_mix_mma_maps_ok(int n_q, int n_kv, int head_dim, int v_dim, int maps) {
+    if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q > 32 || maps < 1 || maps > 2 || (n_q / n_kv) % maps) return 0;
     if (head_dim <= 0 || v_dim <= 0 || head_dim % 16 || v_dim % 16 || v_dim > 128) return 0;
-    return MmaSmem(n_q, n_kv, head_dim, v_dim).bytes <= 220 * 1024 ? 1 : 0;
+    return MmaSmem(n_q, n_kv, head_dim, v_dim, maps * head_dim).bytes <= 220 * 1024 ? 1 : 0;
+}
+extern "C" int kipp_attention_mix_mma_ok(int n_q, int n_kv, int head_dim, int v_dim) {
+    return kipp_attention_mix_mma_maps_ok(n_q, n_kv, head_dim, v_dim, 1);
 }
 extern "C" int kipp_attention_mix_mma_tile() { return QB; }
 
-// work: (entry, first token) per block of 8 tokens, over every entry of the step.
-extern "C" int kipp_attention_mix_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
-                                      const float* head_mix, const int* work, int n_items, const int* q_start,
-                                      const int* context_len, const int* block_table, int table_width,
-                                      int page_size, int n_q, int n_kv, int head_dim, int v_dim, float scale,
-                                      int window, int keep_first, float out_scale, int* status, void* stream) {
+// work: (entry, first token) per block of 8 tokens, over every entry of the step.  extras: score
+// maps, their combination, sink and gate of MixExtras, or null.
+extern "C" int kipp_attention_mix_mma_ex(void* out, const void* q, const void* k_pages, const void* v_pages,
+                                         const float* head_mix, const int* work, int n_items, const int* q_start,
+                                         const int* context_len, const int* block_table, int table_width,
+                                         int page_size, int n_q, int n_kv, int head_dim, int v_dim, float scale,
+                                         int window, int keep_first, float out_scale, const void* extras, int* status,
+                                         void* stream) {
     if (n_items <= 0) return 0;
-    if (!kipp_attention_mix_mma_ok(n_q, n_kv, head_dim, v_dim) || page_size <= 0 || window < 0 || keep_first < 0)
+    MixExtras ex = {};
+    ex.key_maps = 1;
+    if (extras != nullptr) ex = *static_cast<const MixExtras*>(extras);
+    if (ex.values_in_keys || (ex.diff && ex.key_maps != 2) || (ex.key_maps > 1 && head_mix != nullptr)) return KIPP_ERR_ARG;
+    if (!kipp_attention_mix_mma_maps_ok(n_q, n_kv, head_dim, v_dim, ex.key_maps) || page_size <= 0 || window < 0 ||
+        keep_first < 0)
         return KIPP_ERR_ARG;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) != 0) return -3;
-    const size_t smem = MmaSmem(n_q, n_kv, head_dim, v_dim).bytes;
+    const size_t smem = MmaSmem(n_q, n_kv, head_dim, v_dim, ex.key_maps * head_dim).bytes;
     cudaStream_t s = (cudaStream_t)stream;
-    const int hpw = (n_q + 7) / 8, vb = (v_dim + 15) / 16;
+    // heads per warp; with two maps per head a warp owns whole heads, two maps each
+    const int hpw = ex.key_maps == 2 ? 2 * ((n_q / 2 + 7) / 8) : (n_q + 7) / 8, vb = (v_dim + 15) / 16;
 #define KIPP_MIX_MMA(H, V)                                                                                             \
     return launch_mix_mma<H, V>(smem, n_items, s, (bf16*)out, (const bf16*)q, (const bf16*)k_pages,                    \
                                 (const bf16*)v_pages, head_mix, work, q_start, context_len, block_table, table_width,  \
-                                page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, status)
+                                page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, status, ex)
     if (hpw <= 1) { if (vb <= 2) KIPP_MIX_MMA(1, 2); if (vb <= 4) KIPP_MIX_MMA(1, 4); KIPP_MIX_MMA(1, 8); }
     if (hpw <= 2) { if (vb <= 2) KIPP_MIX_MMA(2, 2); if (vb <= 4) KIPP_MIX_MMA(2, 4); KIPP_MIX_MMA(2, 8); }
     if (vb <= 2) KIPP_MIX_MMA(4, 2);
     if (vb <= 4) KIPP_MIX_MMA(4, 4);
     KIPP_MIX_MMA(4, 8);
 #undef KIPP_MIX_MMA
+}
+extern "C" int kipp_attention_mix_mma(void* out, const void* q, const void* k_pages, const void* v_pages,
+                                      const float* head_mix, const int* work, int n_items, const int* q_start,
+                                      const int* context_len, const int* block_table, int table_width,
+                                      int page_size, int n_q, int n_kv, int head_dim, int v_dim, float scale,
+                                      int window, int keep_first, float out_scale, int* status, void* stream) {
+    return kipp_attention_mix_mma_ex(out, q, k_pages, v_pages, head_mix, work, n_items, q_start, context_len, block_table,
+                                     table_width, page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
+                                     out_scale, nullptr, status, stream);
 }
 
 // Runs a step of `tokens` tokens is cut into (1: every token walks its keys in one block): few

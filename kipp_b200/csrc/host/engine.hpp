@@ -1467,6 +1467,7 @@ inline std::string Engine::info_json() {
     counters.set("stream_decode_launches", ops_.stream_decode_launches);
     counters.set("projections_to_heads", ops_.projections_to_heads);
     counters.set("mix_mma_launches", ops_.mix_mma_launches);
+    counters.set("shared_key_launches", ops_.shared_key_launches);
     j.set("counters", std::move(counters));
     info_ = j.dump();
     return info_;

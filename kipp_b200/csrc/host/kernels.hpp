@@ -285,21 +285,24 @@ public:
                            int*, void*);
         using Fr = int (*)(int, int, int, int);
         using Fs = long long (*)(int, int, int, int);
-        using Fo = int (*)(int, int, int, int);
+        using Fo = int (*)(int, int, int, int, int);
         using Fm = int (*)(void*, const void*, const void*, const void*, const float*, const int*, int, const int*,
-                           const int*, const int*, int, int, int, int, int, int, float, int, int, float, int*, void*);
+                           const int*, const int*, int, int, int, int, int, int, float, int, int, float, const void*, int*,
+                           void*);
         static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix_ex");
         static Fr runs_of = kernel_symbol<Fr>("attention_mix", "kipp_attention_mix_runs");
         static Fs scratch_of = kernel_symbol<Fs>("attention_mix", "kipp_attention_mix_scratch_floats");
-        static Fo mma_ok = kernel_symbol<Fo>("attention_mix", "kipp_attention_mix_mma_ok");
-        static Fm mma = kernel_symbol<Fm>("attention_mix", "kipp_attention_mix_mma");
+        static Fo mma_ok = kernel_symbol<Fo>("attention_mix", "kipp_attention_mix_mma_maps_ok");
+        static Fm mma = kernel_symbol<Fm>("attention_mix", "kipp_attention_mix_mma_ex");
         const bool aligned = (((uintptr_t)out | (uintptr_t)q | (uintptr_t)cache.k_pages | (uintptr_t)cache.v_pages) & 15) == 0;
-        const bool plain = extras == nullptr || !extras->any();         // the tensor-core kernel has none of the options
-        if (dtype == BF16 && mix_tensor_core && plain && tokens > MIX_MMA_MIN_TOKENS && tiles != nullptr && n_tiles > 0 &&
-            aligned && mma_ok(n_q, n_kv, head_dim, v_dim)) {
+        // (the tensor-core prompt kernel takes every option but values that lie in their key rows)
+        const bool in_keys = extras != nullptr && extras->values_in_keys;
+        const int maps = extras != nullptr ? extras->key_maps : 1;
+        if (dtype == BF16 && mix_tensor_core && !in_keys && tokens > MIX_MMA_MIN_TOKENS && tiles != nullptr && n_tiles > 0 &&
+            aligned && (maps == 1 || head_mix == nullptr) && mma_ok(n_q, n_kv, head_dim, v_dim, maps)) {
             run(mma(out, q, cache.k_pages, cache.v_pages, head_mix, tiles, n_tiles, q_start, context_len, cache.block_table,
                     cache.table_width, cache.page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale,
-                    status, stream),
+                    extras, status, stream),
                 "attention_mix_mma");
             ++mix_mma_launches;
             return;
@@ -308,6 +311,22 @@ public:
         const int runs = runs_of(tokens, window, keep_first, cache.table_width * cache.page_size);
         float* partial = runs > 1 ? workspace->get<float>("attention_mix_runs", (size_t)scratch_of(tokens, runs, n_q, v_dim))
                                   : nullptr;
+        // one key row per token that is also its value (a latent), all heads on it: the heads of a
+        // token are the rows of a tensor-core tile
+        using Fk = int (*)(int, int, int);
+        using Fsk = int (*)(void*, const void*, const void*, const int*, const int*, const int*, int, int, int, int, int, int,
+                            float, int, float, int, float*, const void*, int*, void*);
+        static Fk shared_ok = kernel_symbol<Fk>("attention_mix", "kipp_attention_shared_key_ok");
+        static Fsk shared = kernel_symbol<Fsk>("attention_mix", "kipp_attention_shared_key");
+        if (dtype == BF16 && mix_tensor_core && extras != nullptr && extras->values_in_keys && extras->key_maps == 1 &&
+            !extras->diff && head_mix == nullptr && n_kv == 1 && keep_first == 0 &&
+            (((uintptr_t)out | (uintptr_t)q | (uintptr_t)cache.k_pages) & 15) == 0 && shared_ok(n_q, head_dim, v_dim)) {
+            run(shared(out, q, cache.k_pages, positions, entry_of_token, cache.block_table, cache.table_width, cache.page_size,
+                       tokens, n_q, head_dim, v_dim, scale, window, out_scale, runs, partial, extras, status, stream),
+                "attention_shared_key", runs > 1 ? 2 : 1);
+            ++shared_key_launches;
+            return;
+        }
         run(f(out, q, cache.k_pages, cache.v_pages, dtype, head_mix, positions, entry_of_token, cache.block_table,
               cache.table_width, cache.page_size, tokens, n_q, n_kv, head_dim, v_dim, scale, window, keep_first,
               out_scale, runs, partial, extras, status, stream),
@@ -673,6 +692,7 @@ public:
     long long stream_decode_launches = 0;   // decode attention dealt out as a stream
     long long projections_to_heads = 0;     // q/k/v projections with norm, rotation and cache write inside
     long long mix_mma_launches = 0;         // launches of the tensor-core kernel of the mixed-head attention
+    long long shared_key_launches = 0;      // launches of the tensor-core kernel for one shared key row per token
 };
 
 }  // namespace kipp

@@ -158,6 +158,14 @@ def test_whole_prompt_and_every_way_of_cutting_it(name, dtype):
     close(cut, want, dtype, "portions")
     if dtype == "float32":
         assert nmse(single.cpu(), whole.cpu()) <= 1e-10 and nmse(cut.cpu(), whole.cpu()) <= 1e-10
+    # in bfloat16 the attention over a latent runs on the tensor-core kernel where the key row is a
+    # multiple of 16 wide and the latent a multiple of 8 (a layer of A, C, D), else on CUDA cores (B)
+    used = eng.info()["counters"]["shared_key_launches"]
+    assert (used > 0) == (dtype == "bfloat16" and name in ("A", "C", "D")), used
+    # and prompt steps of more than 64 tokens of the differential attention on the tensor-core
+    # kernel of the mixed-head attention where the head sizes are multiples of 16 (C)
+    used = eng.info()["counters"]["mix_mma_launches"]
+    assert (used > 0) == (dtype == "bfloat16" and name == "C"), used
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
