@@ -485,11 +485,17 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
                          const bf16* __restrict__ v_pages, const float* __restrict__ head_mix,
                          const int* __restrict__ work, const int* __restrict__ q_start,
                          const int* __restrict__ context_len, const int* __restrict__ block_table, int table_width,
-                         int page_size, int n_q, int n_kv, int head_dim, int v_dim, float scale, int window,
-                         int keep_first, float out_scale, int* __restrict__ status, const MixExtras ex) {
+                         int page_size, int n_q_all, int n_kv_all, int head_dim, int v_dim, float scale, int window,
+                         int keep_first, float out_scale, int* __restrict__ status, const MixExtras ex, int kv_per_block) {
     extern __shared__ __align__(16) unsigned char raw[];
     const int maps = ex.key_maps, k_row = maps * head_dim;
-    const MmaSmem L(n_q, n_kv, head_dim, v_dim, k_row);
+    // Without a mix the kv heads need nothing of one another: blockIdx.y takes kv_per_block of them with
+    // their query heads (n_q, n_kv and every head index below are the block's own; h_first and g_first
+    // lead back to the model's).  With a mix one block holds them all.
+    const int group = n_q_all / n_kv_all;
+    const int g_first = blockIdx.y * kv_per_block, h_first = g_first * group;
+    const int n_kv = min(kv_per_block, n_kv_all - g_first), n_q = n_kv * group;
+    const MmaSmem L(kv_per_block * group, kv_per_block, head_dim, v_dim, k_row);
     // the heads a warp owns: warp, warp + 8, ...; with two maps per head both maps of heads warp, warp + 8, ...
     const bool pairs = maps == 2;
 #define KIPP_OWNED_HEAD(hh) (pairs ? 2 * (warp + 8 * ((hh) >> 1)) + ((hh) & 1) : warp + 8 * (hh))
@@ -515,14 +521,13 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
     const int pos0 = context_len[e] + t0;                           // position of the block's first query
     const int pos_hi = pos0 + n_tok - 1;
     const int* table = block_table + (size_t)e * table_width;
-    const int group = n_q / n_kv;
 
     // the block's queries (zero rows beyond the entry's end), the mix, the running softmax state
     const int qchunks = head_dim / 8;
     for (int i = tid; i < n_q * QB * qchunks; i += MMA_THREADS) {
         const int c = i % qchunks, r = (i / qchunks) % QB, h = i / (qchunks * QB);
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < n_tok) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + r) * n_q + h) * head_dim + c * 8);
+        if (r < n_tok) v = *reinterpret_cast<const uint4*>(q + ((size_t)(row0 + r) * n_q_all + h_first + h) * head_dim + c * 8);
         *reinterpret_cast<uint4*>(qs + ((size_t)h * QB + r) * ldq + c * 8) = v;
     }
     if (head_mix != nullptr)                                        // transposed: mix[g][h], the heads a lane mixes side by side
@@ -560,7 +565,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         for (int rr = tid >> 3; rr < n_kv * KT; rr += MMA_THREADS / 8) {
             const int jj = rr & (KT - 1), g = rr / KT;
             const bool ok = pg[jj] >= 0;
-            const bf16* src = ok ? k_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * k_row : k_pages;
+            const bf16* src = ok ? k_pages + (((size_t)pg[jj] * n_kv_all + g_first + g) * page_size + sl[jj]) * k_row : k_pages;
             const uint32_t dst = smem_address(kv + (size_t)rr * ldkv);
             for (int c = tid & 7; c < kchunks; c += 8) cp_async16(dst + c * 16, ok ? src + c * 8 : src, ok ? 16 : 0);
         }
@@ -605,7 +610,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         for (int rr = tid >> 3; rr < n_kv * KT; rr += MMA_THREADS / 8) {
             const int jj = rr & (KT - 1), g = rr / KT;
             const bool ok = pg[jj] >= 0;
-            const bf16* src = ok ? v_pages + (((size_t)pg[jj] * n_kv + g) * page_size + sl[jj]) * v_dim : v_pages;
+            const bf16* src = ok ? v_pages + (((size_t)pg[jj] * n_kv_all + g_first + g) * page_size + sl[jj]) * v_dim : v_pages;
             const uint32_t dst = smem_address(kv + (size_t)rr * ldkv);
             for (int c = tid & 7; c < vchunks; c += 8) cp_async16(dst + c * 16, ok ? src + c * 8 : src, ok ? 16 : 0);
         }
@@ -732,8 +737,8 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
             float f1[2], f2[2], ss[2] = {0.f, 0.f};
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                f1[c] = softmax_factor(m_run[h * QB + tig * 2 + c], l_run[h * QB + tig * 2 + c], ex.sink, h);
-                f2[c] = softmax_factor(m_run[(h + 1) * QB + tig * 2 + c], l_run[(h + 1) * QB + tig * 2 + c], ex.sink, h + 1);
+                f1[c] = softmax_factor(m_run[h * QB + tig * 2 + c], l_run[h * QB + tig * 2 + c], ex.sink, h_first + h);
+                f2[c] = softmax_factor(m_run[(h + 1) * QB + tig * 2 + c], l_run[(h + 1) * QB + tig * 2 + c], ex.sink, h_first + h + 1);
             }
 #pragma unroll
             for (int vb = 0; vb < VB; ++vb) {
@@ -750,7 +755,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
                 ss[0] += __shfl_xor_sync(0xffffffffu, ss[0], x);
                 ss[1] += __shfl_xor_sync(0xffffffffu, ss[1], x);
             }
-            const int n_out = n_q / 2, ho = h / 2;
+            const int n_out = n_q_all / 2, ho = (h_first + h) / 2;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 if (tig * 2 + c >= n_tok) continue;
@@ -772,23 +777,24 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
     for (int hh = 0; hh < HPW; ++hh) {
         const int h = KIPP_OWNED_HEAD(hh);
         if (h >= n_q) break;
-        float i0 = softmax_factor(m_run[h * QB + tig * 2], l_run[h * QB + tig * 2], ex.sink, h) * out_scale;
-        float i1 = softmax_factor(m_run[h * QB + tig * 2 + 1], l_run[h * QB + tig * 2 + 1], ex.sink, h) * out_scale;
+        const int hm = h_first + h;                                     // the head's index in the model
+        float i0 = softmax_factor(m_run[h * QB + tig * 2], l_run[h * QB + tig * 2], ex.sink, hm) * out_scale;
+        float i1 = softmax_factor(m_run[h * QB + tig * 2 + 1], l_run[h * QB + tig * 2 + 1], ex.sink, hm) * out_scale;
         if (gate != nullptr) {
-            if (tig * 2 < n_tok) i0 *= sigmoid_(to_f32(gate[(size_t)(row0 + tig * 2) * ex.ld_gate + ex.gate_off + h]));
-            if (tig * 2 + 1 < n_tok) i1 *= sigmoid_(to_f32(gate[(size_t)(row0 + tig * 2 + 1) * ex.ld_gate + ex.gate_off + h]));
+            if (tig * 2 < n_tok) i0 *= sigmoid_(to_f32(gate[(size_t)(row0 + tig * 2) * ex.ld_gate + ex.gate_off + hm]));
+            if (tig * 2 + 1 < n_tok) i1 *= sigmoid_(to_f32(gate[(size_t)(row0 + tig * 2 + 1) * ex.ld_gate + ex.gate_off + hm]));
         }
 #pragma unroll
         for (int vb = 0; vb < VB; ++vb) {
             if (vb * 16 >= v_dim) break;
             const int vd = vb * 16 + gid;
             if (tig * 2 < n_tok) {
-                bf16* dst = out + ((size_t)(row0 + tig * 2) * n_q + h) * v_dim;
+                bf16* dst = out + ((size_t)(row0 + tig * 2) * n_q_all + hm) * v_dim;
                 dst[vd] = __float2bfloat16_rn(o[hh][vb][0] * i0);
                 dst[vd + 8] = __float2bfloat16_rn(o[hh][vb][2] * i0);
             }
             if (tig * 2 + 1 < n_tok) {
-                bf16* dst = out + ((size_t)(row0 + tig * 2 + 1) * n_q + h) * v_dim;
+                bf16* dst = out + ((size_t)(row0 + tig * 2 + 1) * n_q_all + hm) * v_dim;
                 dst[vd] = __float2bfloat16_rn(o[hh][vb][1] * i1);
                 dst[vd + 8] = __float2bfloat16_rn(o[hh][vb][3] * i1);
             }
@@ -798,7 +804,7 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
 }
 
 template <int HPW, int VB, typename... Args>
-int launch_mix_mma(size_t smem, int items, cudaStream_t s, Args... args) {
+int launch_mix_mma(size_t smem, int items, int head_blocks, cudaStream_t s, Args... args) {
     auto kernel = attention_mix_mma_kernel<HPW, VB>;
     static size_t allowed = 0;
     if (smem > 48 * 1024 && smem > allowed) {
@@ -806,7 +812,7 @@ int launch_mix_mma(size_t smem, int items, cudaStream_t s, Args... args) {
         if (e != cudaSuccess) { cudaGetLastError(); return (int)e; }
         allowed = smem;
     }
-    return kipp_launch(kernel, dim3((unsigned)items), dim3(MMA_THREADS), smem, s, 1, args...);
+    return kipp_launch(kernel, dim3((unsigned)items, (unsigned)head_blocks), dim3(MMA_THREADS), smem, s, 1, args...);
 }
 
 // ---------------------------------------------------------------------------
@@ -1102,10 +1108,18 @@ extern "C" int kipp_attention_shared_key(void* out, const void* q, const void* k
 }
 
 // Whether the tensor-core prompt kernel takes these sizes (bfloat16 only).
-extern "C" int kipp_attention_mix_mma_maps_ok(int n_q, int n_kv, int head_dim, int v_dim, int maps) {
-    if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || n_q > 32 || maps < 1 || maps > 2 || (n_q / n_kv) % maps) return 0;
+// kv heads a block of the tensor-core prompt kernel takes with their query heads (0: the kernel
+// does not take these sizes): at most 32 score maps and 220 KB of shared memory; with a mix all of them.
+extern "C" int kipp_attention_mix_mma_kv_per_block(int n_q, int n_kv, int head_dim, int v_dim, int maps, int mixed) {
+    if (n_q <= 0 || n_kv <= 0 || n_q % n_kv || maps < 1 || maps > 2 || (n_q / n_kv) % maps) return 0;
     if (head_dim <= 0 || v_dim <= 0 || head_dim % 16 || v_dim % 16 || v_dim > 128) return 0;
-    return MmaSmem(n_q, n_kv, head_dim, v_dim, maps * head_dim).bytes <= 220 * 1024 ? 1 : 0;
+    const int group = n_q / n_kv;
+    for (int kvs = mixed ? n_kv : std::min(n_kv, 32 / std::max(group, 1)); kvs >= (mixed ? n_kv : 1); --kvs)
+        if (kvs * group <= 32 && MmaSmem(kvs * group, kvs, head_dim, v_dim, maps * head_dim).bytes <= 220 * 1024) return kvs;
+    return 0;
+}
+extern "C" int kipp_attention_mix_mma_maps_ok(int n_q, int n_kv, int head_dim, int v_dim, int maps) {
+    return kipp_attention_mix_mma_kv_per_block(n_q, n_kv, head_dim, v_dim, maps, 1) > 0 ? 1 : 0;
 }
 extern "C" int kipp_attention_mix_mma_ok(int n_q, int n_kv, int head_dim, int v_dim) {
     return kipp_attention_mix_mma_maps_ok(n_q, n_kv, head_dim, v_dim, 1);
@@ -1125,18 +1139,19 @@ extern "C" int kipp_attention_mix_mma_ex(void* out, const void* q, const void* k
     ex.key_maps = 1;
     if (extras != nullptr) ex = *static_cast<const MixExtras*>(extras);
     if (ex.values_in_keys || (ex.diff && ex.key_maps != 2) || (ex.key_maps > 1 && head_mix != nullptr)) return KIPP_ERR_ARG;
-    if (!kipp_attention_mix_mma_maps_ok(n_q, n_kv, head_dim, v_dim, ex.key_maps) || page_size <= 0 || window < 0 ||
-        keep_first < 0)
-        return KIPP_ERR_ARG;
+    const int kvs = kipp_attention_mix_mma_kv_per_block(n_q, n_kv, head_dim, v_dim, ex.key_maps, head_mix != nullptr);
+    if (kvs <= 0 || page_size <= 0 || window < 0 || keep_first < 0) return KIPP_ERR_ARG;
     if ((((uintptr_t)q | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) != 0) return -3;
-    const size_t smem = MmaSmem(n_q, n_kv, head_dim, v_dim, ex.key_maps * head_dim).bytes;
+    const int n_q_blk = kvs * (n_q / n_kv), head_blocks = (n_kv + kvs - 1) / kvs;
+    const size_t smem = MmaSmem(n_q_blk, kvs, head_dim, v_dim, ex.key_maps * head_dim).bytes;
     cudaStream_t s = (cudaStream_t)stream;
     // heads per warp; with two maps per head a warp owns whole heads, two maps each
-    const int hpw = ex.key_maps == 2 ? 2 * ((n_q / 2 + 7) / 8) : (n_q + 7) / 8, vb = (v_dim + 15) / 16;
+    const int hpw = ex.key_maps == 2 ? 2 * ((n_q_blk / 2 + 7) / 8) : (n_q_blk + 7) / 8, vb = (v_dim + 15) / 16;
 #define KIPP_MIX_MMA(H, V)                                                                                             \
-    return launch_mix_mma<H, V>(smem, n_items, s, (bf16*)out, (const bf16*)q, (const bf16*)k_pages,                    \
+    return launch_mix_mma<H, V>(smem, n_items, head_blocks, s, (bf16*)out, (const bf16*)q, (const bf16*)k_pages,       \
                                 (const bf16*)v_pages, head_mix, work, q_start, context_len, block_table, table_width,  \
-                                page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, status, ex)
+                                page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale, status, ex, \
+                                kvs)
     if (hpw <= 1) { if (vb <= 2) KIPP_MIX_MMA(1, 2); if (vb <= 4) KIPP_MIX_MMA(1, 4); KIPP_MIX_MMA(1, 8); }
     if (hpw <= 2) { if (vb <= 2) KIPP_MIX_MMA(2, 2); if (vb <= 4) KIPP_MIX_MMA(2, 4); KIPP_MIX_MMA(2, 8); }
     if (vb <= 2) KIPP_MIX_MMA(4, 2);

@@ -285,21 +285,22 @@ public:
                            int*, void*);
         using Fr = int (*)(int, int, int, int);
         using Fs = long long (*)(int, int, int, int);
-        using Fo = int (*)(int, int, int, int, int);
+        using Fo = int (*)(int, int, int, int, int, int);
         using Fm = int (*)(void*, const void*, const void*, const void*, const float*, const int*, int, const int*,
                            const int*, const int*, int, int, int, int, int, int, float, int, int, float, const void*, int*,
                            void*);
         static Fn f = kernel_symbol<Fn>("attention_mix", "kipp_attention_mix_ex");
         static Fr runs_of = kernel_symbol<Fr>("attention_mix", "kipp_attention_mix_runs");
         static Fs scratch_of = kernel_symbol<Fs>("attention_mix", "kipp_attention_mix_scratch_floats");
-        static Fo mma_ok = kernel_symbol<Fo>("attention_mix", "kipp_attention_mix_mma_maps_ok");
+        static Fo mma_ok = kernel_symbol<Fo>("attention_mix", "kipp_attention_mix_mma_kv_per_block");
         static Fm mma = kernel_symbol<Fm>("attention_mix", "kipp_attention_mix_mma_ex");
         const bool aligned = (((uintptr_t)out | (uintptr_t)q | (uintptr_t)cache.k_pages | (uintptr_t)cache.v_pages) & 15) == 0;
         // (the tensor-core prompt kernel takes every option but values that lie in their key rows)
         const bool in_keys = extras != nullptr && extras->values_in_keys;
         const int maps = extras != nullptr ? extras->key_maps : 1;
         if (dtype == BF16 && mix_tensor_core && !in_keys && tokens > MIX_MMA_MIN_TOKENS && tiles != nullptr && n_tiles > 0 &&
-            aligned && (maps == 1 || head_mix == nullptr) && mma_ok(n_q, n_kv, head_dim, v_dim, maps)) {
+            aligned && (maps == 1 || head_mix == nullptr) &&
+            mma_ok(n_q, n_kv, head_dim, v_dim, maps, head_mix != nullptr ? 1 : 0) > 0) {
             run(mma(out, q, cache.k_pages, cache.v_pages, head_mix, tiles, n_tiles, q_start, context_len, cache.block_table,
                     cache.table_width, cache.page_size, n_q, n_kv, head_dim, v_dim, scale, window, keep_first, out_scale,
                     extras, status, stream),

@@ -32,7 +32,7 @@
 // float32 (q/r, k, and for the delta rule w, a * u, u) in a workspace; fully parallel over the
 // step's tokens.  (2) scan: a block per (entry, head, slice of 32 value columns) -- the columns
 // of S evolve independently -- walks the entry's tokens in order; a thread owns one column and a
-// run of at most 32 key rows in registers (P = 1, 2, 4 or 8 threads per column, neighbours in a
+// run of at most 32 key rows in registers (P = 1, 2, 4, 8 or 16 threads per column, neighbours in a
 // warp, their partial sums met by shuffles); the token vectors come through shared memory in
 // batches.  The state is read from and written back to its slot once per launch; a decoded token
 // is a batch of one.  (3) finish: a warp per (token, head) divides by the root mean square,
@@ -321,9 +321,9 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     const int D = a.dim, V = a.v_dim + Rec<DELTA>::XV;
     constexpr int NV = Rec<DELTA>::NV, XG = Rec<DELTA>::XG;
     // threads per column: runs of 8 key rows where the head allows (short chains of dependent
-    // multiply-adds, more warps per block), at most 8 threads
+    // multiply-adds, more warps per block), at most 16 threads
     int P = 1;
-    while (P < 8 && (D + P - 1) / P > 8) P *= 2;
+    while (P < 16 && (D + P - 1) / P > 8) P *= 2;
     if ((D + P - 1) / P > MAX_CHUNK || scratch == nullptr) return KIPP_ERR_ARG;
     const size_t per_token = ((size_t)NV * D + XG + VS) * sizeof(float);
     int batch = (int)std::min<size_t>(32, (20 * 1024) / per_token);       // two buffers of at most 20 KB
@@ -343,7 +343,8 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     case 1: rc = launch_scan_chunk<T, DELTA, 1>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
     case 2: rc = launch_scan_chunk<T, DELTA, 2>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
     case 4: rc = launch_scan_chunk<T, DELTA, 4>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
-    default: rc = launch_scan_chunk<T, DELTA, 8>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
+    case 8: rc = launch_scan_chunk<T, DELTA, 8>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
+    default: rc = launch_scan_chunk<T, DELTA, 16>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
     }
     if (rc) return rc;
     return kipp_launch(recurrent_finish_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, (const float*)o_raw, tokens);
@@ -363,7 +364,7 @@ __global__ void tanh_rows_kernel(T* __restrict__ out, long long ld_out, const T*
 
 // Whether the scan kernels take a head of these sizes.
 extern "C" int kipp_recurrent_scan_ok(int dim, int v_dim, int kind) {
-    if (dim <= 0 || v_dim <= 0 || dim > 8 * MAX_CHUNK || kind < 0 || kind > 2) return 0;
+    if (dim <= 0 || v_dim <= 0 || dim > 16 * MAX_CHUNK || kind < 0 || kind > 2) return 0;
     return (((kind == DELTA_RULE ? 5 : 2) * (size_t)dim + 4 + VS) * sizeof(float)) <= 20 * 1024 ? 1 : 0;
 }
 // float32 values of scratch a scan of `tokens` tokens needs.
