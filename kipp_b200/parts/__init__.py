@@ -1,14 +1,16 @@
 from .attention import AttentionMixer
 from .base import (Block, EmbeddingStage, FeedForward, Mixer, Norm, PagedKVSpec, Part, PlanContext,
                    PositionEncoding, StateSpec)
-from .block import PreNormBlock
+from .block import ParallelBlock, PreNormBlock
+from .latent import LatentAttentionMixer
 from .embedding import OutputHead, TokenEmbedding
-from .mlp import SwiGLUFeedForward
-from .norm import RMSNorm
-from .recurrent import DeltaRuleMixer, ParallelMixer, PolyNormFeedForward, RetentionMixer
-from .rope import NoPositionEncoding, RotaryEncoding
+from .mlp import DenseFeedForward, SwiGLUFeedForward
+from .norm import LayerNorm, RMSNorm
+from .recurrent import DeltaRuleMixer, GatedMemoryMixer, ParallelMixer, PolyNormFeedForward, RetentionMixer
+from .rope import NoPositionEncoding, RotaryEncoding, StretchedRotaryEncoding
 
 __all__ = ["AttentionMixer", "Block", "EmbeddingStage", "FeedForward", "Mixer", "Norm", "PagedKVSpec", "Part",
            "PlanContext", "PositionEncoding", "StateSpec", "PreNormBlock", "OutputHead", "TokenEmbedding",
            "SwiGLUFeedForward", "RMSNorm", "NoPositionEncoding", "RotaryEncoding", "DeltaRuleMixer", "ParallelMixer",
-           "PolyNormFeedForward", "RetentionMixer"]
+           "PolyNormFeedForward", "RetentionMixer", "ParallelBlock", "LatentAttentionMixer", "DenseFeedForward",
+           "LayerNorm", "GatedMemoryMixer", "StretchedRotaryEncoding"]

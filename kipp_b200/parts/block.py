@@ -21,3 +21,19 @@ class PreNormBlock(Block):
         described = [None if p is None else p.describe(prefix + n, ctx) for p, n in zip(parts, self.names)]
         return {"names": list(self.names), "input_norm": described[0], "mixer": described[1],
                 "post_norm": described[2], "ffn": described[3]}
+
+
+class ParallelBlock(Block):
+    """x += mixer(n) + ffn(n) with n = norm(x): ONE norm whose output both
+    sublayers read.  ``ffn`` None: the mixer only.  The part itself:
+    csrc/host/parts.hpp."""
+    kind = "parallel_block"
+
+    def __init__(self, norm: Norm, mixer: Mixer, ffn: FeedForward, names: tuple[str, str, str] = ("norm.", "mix.", "mlp.")):
+        self.norm, self.mixer, self.ffn = norm, mixer, ffn
+        self.names = tuple(names)
+
+    def params(self, prefix, ctx) -> dict:
+        parts = (self.norm, self.mixer, self.ffn)
+        described = [None if p is None else p.describe(prefix + n, ctx) for p, n in zip(parts, self.names)]
+        return {"names": list(self.names), "norm": described[0], "mixer": described[1], "ffn": described[2]}

@@ -13,12 +13,13 @@ from .base import EmbeddingStage, Part
 class TokenEmbedding(EmbeddingStage):
     kind = "token_embedding"
 
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str = "weight"):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
+        self.weight_name = weight_name
 
     def params(self, prefix, ctx) -> dict:
-        return {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size}
+        return {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "weight_name": self.weight_name}
 
 
 class OutputHead(Part):
@@ -26,10 +27,12 @@ class OutputHead(Part):
     in when the checkpoint has no head of its own."""
     kind = "output_head"
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None, weight_name: str = "weight"):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
+        self.weight_name = weight_name
 
     def params(self, prefix, ctx) -> dict:
-        return {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied_to": self.tied_to}
+        return {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied_to": self.tied_to,
+                "weight_name": self.weight_name}

@@ -1,5 +1,6 @@
 """RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, computed in float32
-(src/kipp.c:2221-2231).  The part itself: csrc/host/parts.hpp."""
+(src/kipp.c:2221-2231), and the layer norm y = (x - mean) / sqrt(var + eps) * w + b.
+The parts themselves: csrc/host/parts.hpp."""
 from __future__ import annotations
 
 from .base import Norm
@@ -15,3 +16,16 @@ class RMSNorm(Norm):
 
     def params(self, prefix, ctx) -> dict:
         return {"size": self.size, "eps": self.eps, "weight_name": self.weight_name}
+
+
+class LayerNorm(Norm):
+    """``bias_name`` empty: no bias."""
+    kind = "layernorm"
+
+    def __init__(self, size: int, eps: float, weight_name: str = "weight", bias_name: str = "bias"):
+        self.size = size
+        self.eps = float(eps)
+        self.weight_name, self.bias_name = weight_name, bias_name
+
+    def params(self, prefix, ctx) -> dict:
+        return {"size": self.size, "eps": self.eps, "weight_name": self.weight_name, "bias_name": self.bias_name}

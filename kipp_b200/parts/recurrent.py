@@ -5,6 +5,8 @@ csrc/host/recurrent_parts.hpp; their kernels: csrc/recurrent.cu.
 ``RetentionMixer``      S_t = decay_h S_{t-1} + k_t v_t^T, o_t = S_t^T q_t per head (q, k rotated,
                         k scaled), each head's o divided by its root mean square, gated, projected.
 ``DeltaRuleMixer``      S_t = diag(w_t) S_{t-1} - (a_t u_t)(u_t^T S_{t-1}) + k_t v_t^T, o_t = S_t^T r_t.
+``GatedMemoryMixer``    m_t = max(f_t + m_{t-1}, i_t), S_t = e^(f_t + m_{t-1} - m_t) S_{t-1} + e^(i_t - m_t) k_t v_t^T,
+                        n_t alike, o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6): the matrix memory of the xLSTM.
 ``ParallelMixer``       the sum of its branches, each with its own cache or state and output_scale.
 ``PolyNormFeedForward`` W_down (c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3), z = W_up h.
 """
@@ -72,3 +74,22 @@ class PolyNormFeedForward(FeedForward):
     def params(self, prefix, ctx) -> dict:
         return {"hidden_size": self.hidden_size, "intermediate_size": self.intermediate_size, "eps": self.eps,
                 "names": self.names}
+
+
+class GatedMemoryMixer(Mixer):
+    kind = "gated_memory"
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, gate_cap: float, eps: float, *,
+                 value_dim: Optional[int] = None, gate: str = "sigmoid", output_scale: float = 1.0,
+                 query_scale: Optional[float] = None, names: Optional[dict] = None):
+        self.hidden_size, self.num_heads, self.head_dim = hidden_size, num_heads, head_dim
+        self.gate_cap, self.eps, self.value_dim = float(gate_cap), eps, value_dim or head_dim
+        self.gate, self.output_scale, self.query_scale, self.names = gate, output_scale, query_scale, dict(names or {})
+
+    def params(self, prefix, ctx) -> dict:
+        out = {"hidden_size": self.hidden_size, "num_heads": self.num_heads, "head_dim": self.head_dim,
+               "value_dim": self.value_dim, "gate_cap": self.gate_cap, "eps": self.eps, "gate": self.gate,
+               "output_scale": float(self.output_scale), "names": self.names}
+        if self.query_scale is not None:
+            out["query_scale"] = float(self.query_scale)
+        return out

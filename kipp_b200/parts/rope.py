@@ -44,3 +44,36 @@ class NoPositionEncoding(PositionEncoding):
 
     def inv_freq(self, device=None):
         return None
+
+
+class StretchedRotaryEncoding(RotaryEncoding):
+    """Rotary frequencies whose long wavelengths are stretched (the frequency
+    scaling of Llama 3.1): with l = 2 pi / f, f stays where l < original / high,
+    becomes f / factor where l > original / low, and is blended in between."""
+    kind = "stretched_rotary"
+
+    def __init__(self, head_dim: int, theta: float, factor: float, low: float, high: float, original: float,
+                 rotary_dim: Optional[int] = None):
+        super().__init__(head_dim, theta, rotary_dim)
+        self.factor, self.low, self.high, self.original = float(factor), float(low), float(high), float(original)
+
+    def frequencies(self) -> torch.Tensor:
+        import math
+        out = []
+        for i in range(self.rotary_dim // 2):
+            f = self.theta ** (-2.0 * i / self.rotary_dim)
+            wave = 2.0 * math.pi / f
+            if wave > self.original / self.low:
+                f /= self.factor
+            elif not wave < self.original / self.high:
+                s = (self.original / wave - self.low) / (self.high - self.low)
+                f = (1.0 - s) * f / self.factor + s * f
+            out.append(f)
+        return torch.tensor(out, dtype=torch.float64).float()
+
+    def table_key(self):
+        return ("stretched", self.theta, self.rotary_dim, self.factor, self.low, self.high, self.original)
+
+    def describe(self, prefix, ctx) -> dict:
+        return {"kind": "stretched_rotary", "head_dim": self.head_dim, "theta": self.theta, "rotary_dim": self.rotary_dim,
+                "factor": self.factor, "low": self.low, "high": self.high, "original": self.original}

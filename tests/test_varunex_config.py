@@ -142,3 +142,41 @@ def test_the_plain_attentions_are_causal():
     full = P.forward(cfg, w, toks)
     assert torch.allclose(P.forward(cfg, w, toks[:9]), full[:9], atol=1e-12)
     assert P.causal(4, 2).int().tolist() == [[1, 0, 0, 0], [1, 1, 0, 0], [0, 1, 1, 0], [0, 0, 1, 1]]
+
+
+def test_the_parts_can_be_described_from_python_for_another_design():
+    """A model put together in Python from the descriptions of the same parts gives
+    the plan the library's own builder makes (apart from the configuration kept in it)."""
+    from kipp_b200.models.spec import LayerRun, ModelSpec
+    from kipp_b200.parts import (AttentionMixer, DenseFeedForward, GatedMemoryMixer, LatentAttentionMixer, LayerNorm,
+                                 OutputHead, ParallelBlock, RotaryEncoding, StretchedRotaryEncoding, TokenEmbedding)
+    cfg = CONFIGS["A"]
+    eps, width = cfg["norm"]["eps"], cfg["width"]
+    layers = []
+    for i, layer in enumerate(cfg["layers"]):
+        m = layer["mixer"]
+        if layer["type"] == "mlstm":
+            mixer = GatedMemoryMixer(width, m["heads"], m["dim"], m["gate_cap"], eps, value_dim=m["vdim"])
+        elif layer["type"] == "latent_attention":
+            mixer = LatentAttentionMixer(width, m["heads"], m["dim"], m["rot_dim"], m["kv_rank"], m["q_rank"],
+                                         RotaryEncoding(m["rot_dim"], m["rot"]["base"]), eps, value_dim=m["vdim"],
+                                         scale=m["scale"], sink=True, gate="sigmoid")
+        else:
+            sc = m["rot"].get("scaling")
+            pos = (StretchedRotaryEncoding(m["dim"], m["rot"]["base"], sc["factor"], sc["low"], sc["high"], sc["original"],
+                                           m["rot"]["dims"]) if sc else RotaryEncoding(m["dim"], m["rot"]["base"], m["rot"]["dims"]))
+            names = {"q": "q", "k": "k", "v": "v", "o": "o", "q_bias": "q.b", "k_bias": "k.b", "v_bias": "v.b",
+                     "lq1": "lq1", "lk1": "lk1", "lq2": "lq2", "lk2": "lk2"}
+            mixer = AttentionMixer(width, m["heads"], m["kv_heads"], m["dim"], pos, None, (m.get("mask") or {}).get("size", 0),
+                                   m["scale"], value_dim=m["vdim"], bias=True, score_maps=2, combine_maps=True,
+                                   lambda_init=m["diff"], combine_eps=eps, names=names)
+        ffn = DenseFeedForward(width, layer["mlp"]["ff"]) if layer["mlp"] else None
+        layers.append((f"l{i}.", ParallelBlock(LayerNorm(width, eps, "norm1", "norm1.b"), mixer, ffn, ("", "mix.", "mlp."))))
+    spec = ModelSpec(config=None, hidden_size=width, vocab_size=cfg["vocab"],
+                     embedding=TokenEmbedding(cfg["vocab"], width, weight_name="embed"), layers=layers,
+                     order=[LayerRun(i, i) for i in range(len(layers))],
+                     final_norm=("", LayerNorm(width, eps, "final.norm", "final.norm.b")),
+                     head=("", OutputHead(cfg["vocab"], width, tied_to=None, weight_name="head")))
+    mine = {s.name: tuple(s.shape) for s in spec.tensor_specs()}
+    theirs = {s.name: tuple(s.shape) for s in spec_of(cfg).tensor_specs()}
+    assert mine == theirs
