@@ -44,6 +44,17 @@ __device__ __forceinline__ float load_w(const void* p, int dtype, size_t i) {
                                 : __bfloat162float(reinterpret_cast<const bf16*>(p)[i]);
 }
 
+// Activations by code, arithmetic in float32: 0 relu, 1 the square of relu, 2 gelu in its tanh
+// form 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 3 silu.
+__device__ __forceinline__ float kipp_activation(float z, int kind) {
+    switch (kind) {
+    case 0: return fmaxf(z, 0.f);
+    case 1: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
+    default: return z / (1.0f + expf(-z));
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -273,14 +273,6 @@ extern "C" int kipp_layernorm(void* out, int out_dtype, const float* x, const fl
 // Activations applied element by element to z [rows, n] in the compute type, arithmetic in
 // float32: 0 relu, 1 the square of relu, 2 gelu with the tanh form
 // 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 3 silu.
-__device__ __forceinline__ float activation_value(float z, int kind) {
-    switch (kind) {
-    case 0: return fmaxf(z, 0.f);
-    case 1: { const float r = fmaxf(z, 0.f); return r * r; }
-    case 2: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * z * z, z, z)));
-    default: return z / (1.0f + expf(-z));
-    }
-}
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ out, long long ld_out, const T* __restrict__ z, long long ld_z,
                                   int rows, int n, int kind) {
@@ -289,7 +281,7 @@ __global__ void activation_kernel(T* __restrict__ out, long long ld_out, const T
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)rows * n) return;
     const long long r = i / n, c = i % n;
-    out[r * ld_out + c] = from_f32<T>(activation_value(to_f32(z[r * ld_z + c]), kind));
+    out[r * ld_out + c] = from_f32<T>(kipp_activation(to_f32(z[r * ld_z + c]), kind));
 }
 
 extern "C" int kipp_activation(void* out, long long ld_out, const void* z, long long ld_z, int dtype, int rows,

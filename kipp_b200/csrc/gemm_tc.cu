@@ -275,7 +275,7 @@ constexpr int SINK_HEAD = 128;
 struct Params {
     void* C;
     int out_dtype;          // KIPP_DT_*
-    int epilogue;
+    int epilogue;           // EPI_*; a store may carry an activation: EPI_STORE | (code + 1) << 8 (kipp_activation)
     int tokens, features, K;
     long long ldc;
     int k_blocks_per_split; // TILE_K blocks each split handles
@@ -311,6 +311,10 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, float* v, int t_
     if (rstd != nullptr) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] *= rstd[j];
+    }
+    if (p.epilogue >> 8) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = kipp_activation(v[j], (p.epilogue >> 8) - 1);
     }
     if (p.epilogue == EPI_ADD) {
         // all loads of the residual first, then the stores: the loads overlap
@@ -607,6 +611,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int s = 0; s < 8; ++s) v += part[s];              // in split order; absent splits add zero
                 if (p.ssq_in != nullptr) v *= rstd_s[j];
+                if (p.epilogue >> 8) v = kipp_activation(v, (p.epilogue >> 8) - 1);
                 const int t = t0 + j;
                 // one value per thread: the epilogue of a 16-token chunk with one live token
                 if (p.epilogue == EPI_SWIGLU) {
@@ -921,6 +926,10 @@ __device__ __forceinline__ void tokm_epilogue_tile(const Params& p, const CUtens
             if (p.ssq_in != nullptr) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] *= rstd;
+            }
+            if (p.epilogue >> 8) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = kipp_activation(v[j], (p.epilogue >> 8) - 1);
             }
             if (ok) epilogue_row16(p, v, t, f0 + c);
         }
@@ -1564,6 +1573,7 @@ int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens
     if ((ldx % 8) || (ldw % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -3;
     if (epilogue == EPI_ADD && out_dtype != KIPP_DT_F32) return KIPP_ERR_DTYPE;
     if (epilogue == EPI_SWIGLU && (features & 1)) return KIPP_ERR_ARG;
+    if ((epilogue >> 8) != 0 && ((epilogue & 0xff) != EPI_STORE || (epilogue >> 8) > 4 || epilogue < 0)) return KIPP_ERR_ARG;
     if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
     // Prompt-sized batches: tokens as the M operand (want_tile_f < 0 forces it with
     // the feature tile -want_tile_f).  The residual add needs a tensor map over C.

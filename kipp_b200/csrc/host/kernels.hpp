@@ -182,16 +182,21 @@ public:
         run(f(out, out_dtype, ssq, x, w, w_dtype, rows, n_rows, size, stream), "rmsnorm_deferred");
     }
 
+    // `activation` (an Activation, or -1 for none) is applied to a stored product: inside the
+    // tensor-core kernel's epilogue on the float32 sums, else by the element-wise kernel afterwards.
     void gemm(void* out, int out_dtype, long long ldc, const void* a, long long lda, const void* w, long long ldw,
-              int dtype, int M, int N, int K, Epilogue epilogue, const NormFold* fold = nullptr) {
+              int dtype, int M, int N, int K, Epilogue epilogue, const NormFold* fold = nullptr, int activation = -1) {
         if (M <= 0 || N <= 0) return;
+        if (activation >= 0 && (epilogue != EPI_STORE || out_dtype != dtype))
+            fail(KIPP_E_STATE, "only a stored product of the compute type can carry an activation");
         if (fold != nullptr && !(gemm_scale_ok(dtype, a, lda, w, ldw) && (fold->norm_w == nullptr || gemm_emit_ok(M))))
             fail(KIPP_E_STATE, "a product was asked to fold a norm that its kernel cannot fold");   // parts ask first
         if (gemm_tc_ok(dtype, a, lda, w, ldw)) {
             using Fn = int (*)(void*, int, const void*, const void*, int, int, int, long long, long long, long long, int,
                                int, int, int, const NormFold*, int*, void*);
             static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_fold");
-            run(f(out, out_dtype, a, w, M, N, K, lda, ldw, ldc, (int)epilogue, 0, 0, 0, fold, status, stream), "gemm_tc", 1,
+            const int code = (int)epilogue | (activation >= 0 ? (activation + 1) << 8 : 0);
+            run(f(out, out_dtype, a, w, M, N, K, lda, ldw, ldc, code, 0, 0, 0, fold, status, stream), "gemm_tc", 1,
                 profiling ? format("gemm_tc %d x %d", N, K).c_str() : nullptr);
             if (fold != nullptr && fold->ssq_in != nullptr) ++folded_norms;
         } else {
@@ -199,6 +204,7 @@ public:
             static Fn f = kernel_symbol<Fn>("gemm_simt", "kipp_gemm_simt");
             run(f(out, out_dtype, a, w, dtype, M, N, K, (int)lda, (int)ldw, (int)ldc, (int)epilogue, stream),
                 "gemm_simt");
+            if (activation >= 0) this->activation(out, ldc, out, ldc, out_dtype, M, N, activation);
         }
     }
 

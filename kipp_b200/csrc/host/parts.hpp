@@ -724,8 +724,8 @@ public:
         NormFold in, out;
         void* z = ctx.workspace->buffer("ffn_up", (size_t)T * ld_ * ctx.element());
         if (ld_ != inter_) cuda_check(cudaMemsetAsync(z, 0, (size_t)T * ld_ * ctx.element(), ctx.stream), "clearing the padding");
-        ctx.ops->gemm(z, ctx.dtype, ld_, h, hidden_, w_up_, hidden_, dtype_, T, inter_, hidden_, EPI_STORE, fold_input(ctx, in));
-        ctx.ops->activation(z, ld_, z, ld_, ctx.dtype, T, inter_, act_);
+        // the activation rides in the product's epilogue where the tensor-core kernel runs it
+        ctx.ops->gemm(z, ctx.dtype, ld_, h, hidden_, w_up_, hidden_, dtype_, T, inter_, hidden_, EPI_STORE, fold_input(ctx, in), act_);
         const NormFold* emit = fold_emit(ctx, out, hidden_);
         ctx.ops->gemm(residual, F32, hidden_, z, ld_, w_down_, ld_, dtype_, T, hidden_, ld_, EPI_ADD, emit);
         fold_emitted(ctx, emit, hidden_);
