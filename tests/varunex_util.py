@@ -61,14 +61,22 @@ CONFIGS = {
                      latent_layer(4, 32, 16, 32, 64, 48, 192, base=1e5),
                      memory_layer(2, 64, 128, 15.0, None),
                      latent_layer(2, 64, 64, 128, 128, 96, 128, base=1e4, scale=0.1)]},
-    # every count that can be 1 is 1, and sizes that can be equal are equal
-    "D": {"architecture": "Varunex", "vocab": 64, "width": 32, "norm": {"eps": 1e-5},
+    # every count that can be 1 is 1, and sizes that can be equal are equal (an odd vocabulary on a
+    # width the tensor-core products take)
+    "D": {"architecture": "Varunex", "vocab": 67, "width": 32, "norm": {"eps": 1e-5},
           "layers": [latent_layer(1, 16, 16, 16, 16, 16, 32),
                      diff_layer(1, 1, 16, 16, 16, 16, 32, diff=0.5),
                      memory_layer(1, 16, 16, 1.0, 32)]},
+    # a width the tensor-core products take around inner sizes that fit no vector width: products
+    # with 86, 30 or 50 features, rows of activations that start at odd addresses
+    "E": {"architecture": "Varunex", "vocab": 67, "width": 64, "norm": {"eps": 1e-5},
+          "layers": [diff_layer(3, 1, 10, 6, 9, 6, 50, diff=0.45),
+                     latent_layer(3, 6, 4, 5, 12, 10, 36, scale=0.8),
+                     memory_layer(1, 12, 7, 9.0, None),
+                     latent_layer(5, 8, 8, 8, 24, 20, 30)]},
 }
 INIT = {"A": dict(seed=3, sigma=0.15, norm_jitter=0.2), "B": dict(seed=5, sigma=0.2, norm_jitter=0.1),
-        "C": dict(seed=9, sigma=0.08, norm_jitter=0.15), "D": dict(seed=12, sigma=0.2, norm_jitter=0.1)}
+        "C": dict(seed=9, sigma=0.08, norm_jitter=0.15), "D": dict(seed=12, sigma=0.2, norm_jitter=0.1), "E": dict(seed=15, sigma=0.2, norm_jitter=0.1)}
 
 _tmp = tempfile.TemporaryDirectory(prefix="kipp_b200_varunex_")
 
