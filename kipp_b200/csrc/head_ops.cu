@@ -15,9 +15,10 @@
 // states its layout as data: keys made of parts, biases, rotation of a head's tail.
 //
 // kipp_head_matmul: out[t, h, :] = W_h a[t, h, :] for every head h, W_h [n, k] row-major, with
-// float32 accumulation on the CUDA cores; the sum over k runs in the same order whatever the
-// number of tokens is.  (Products with a latent: keys absorbed into queries, values expanded
-// after the weighted sum.)
+// float32 accumulation, all heads in one launch: few tokens by a kernel that reads the weights
+// once, many tokens in bfloat16 on the tensor cores (mma.sync), the rest in tiles on the CUDA
+// cores.  (Products with a latent: keys absorbed into queries, values expanded after the
+// weighted sum.)
 #include "common.cuh"
 #include <math.h>
 
@@ -207,6 +208,76 @@ head_matvec_kernel(T* __restrict__ C, const T* __restrict__ A, const T* __restri
     }
 }
 
+// Many tokens in bfloat16: the same product on the tensor cores (mma.sync m16n8k16), all heads in one
+// launch.  A block of 4 warps takes 64 tokens x 64 features of one head; K is walked in steps of 32
+// through shared memory (16-byte asynchronous copies, zeros beyond M, N and K); a warp owns 16
+// tokens x 64 features.  The sum over k runs in the same order for every token.
+constexpr int HM = 64, HN = 64, HK = 32, HLD = HK + 8;
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__global__ void __launch_bounds__(128)
+head_matmul_mma_kernel(bf16* __restrict__ C, const bf16* __restrict__ A, const bf16* __restrict__ W, int M, int N, int K,
+                       long long lda, long long a_head, long long w_head, long long ldc, long long c_head) {
+    __shared__ __align__(16) bf16 As[HM * HLD];
+    __shared__ __align__(16) bf16 Ws[HN * HLD];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.z;
+    A += (size_t)h * a_head;
+    W += (size_t)h * w_head;
+    C += (size_t)h * c_head;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+    const int m0 = blockIdx.y * HM, n0 = blockIdx.x * HN;
+    float acc[HN / 8][4];
+#pragma unroll
+    for (int j = 0; j < HN / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HK) {
+        __syncthreads();                                            // the step before has read its tiles
+        // 64 rows x 4 chunks of 8 elements for each operand: 256 chunks, two per thread and operand
+        for (int i = tid; i < HM * (HK / 8); i += 128) {
+            const int r = i >> 2, c = (i & 3) * 8;
+            const bool ka = k0 + c < K;
+            const bool oa = ka && m0 + r < M, ow = ka && n0 + r < N;
+            cp_async16(smem_address(As + r * HLD + c), oa ? A + (size_t)(m0 + r) * lda + k0 + c : A, oa ? 16 : 0);
+            cp_async16(smem_address(Ws + r * HLD + c), ow ? W + (size_t)(n0 + r) * K + k0 + c : W, ow ? 16 : 0);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < HK; ks += 16) {
+            const bf16* ar = As + (warp * 16 + gid) * HLD + ks + tig * 2;
+            uint32_t a[4];
+            a[0] = *reinterpret_cast<const uint32_t*>(ar);
+            a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * HLD);
+            a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+            a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * HLD + 8);
+#pragma unroll
+            for (int j = 0; j < HN / 8; ++j) {
+                const bf16* wr = Ws + (j * 8 + gid) * HLD + ks + tig * 2;
+                mma_bf16_16816(acc[j], a, *reinterpret_cast<const uint32_t*>(wr), *reinterpret_cast<const uint32_t*>(wr + 8));
+            }
+        }
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int m = m0 + warp * 16 + gid + 8 * half;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < HN / 8; ++j) {
+            const int n = n0 + j * 8 + tig * 2;
+            if (n + 1 < N) {
+                *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + n) = __floats2bfloat162_rn(acc[j][2 * half], acc[j][2 * half + 1]);
+            } else if (n < N) {
+                C[(size_t)m * ldc + n] = __float2bfloat16_rn(acc[j][2 * half]);
+            }
+        }
+    }
+}
+
 // out[h][n][k] = in[h][k][n]: the matrices of every head transposed (at bind time).
 template <typename T>
 __global__ void transpose_heads_kernel(T* __restrict__ out, const T* __restrict__ in, int rows, int cols) {
@@ -220,6 +291,15 @@ __global__ void transpose_heads_kernel(T* __restrict__ out, const T* __restrict_
 template <typename T>
 int launch_head_matmul(void* C, const void* A, const void* W, int M, int N, int K, int heads, long long lda,
                        long long a_head, long long w_head, long long ldc, long long c_head, cudaStream_t s) {
+    // the tensor-core kernel: bfloat16, more tokens than the weight-streaming kernel takes, rows of
+    // both operands on 16-byte boundaries, results on 4-byte ones
+    if (sizeof(T) == 2 && M > 2 * MT && K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 && w_head % 8 == 0 && ldc % 2 == 0 &&
+        c_head % 2 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && ((uintptr_t)C & 3) == 0) {
+        const dim3 grid((unsigned)((N + HN - 1) / HN), (unsigned)((M + HM - 1) / HM), (unsigned)heads);
+        if (grid.y > 65535) return KIPP_ERR_ARG;
+        return kipp_launch(head_matmul_mma_kernel, grid, dim3(128), 0, s, 1, (bf16*)C, (const bf16*)A, (const bf16*)W, M, N, K,
+                           lda, a_head, w_head, ldc, c_head);
+    }
     if (M <= 2 * MT) {
         const dim3 grid((unsigned)((N + 7) / 8), (unsigned)((M + MT - 1) / MT), (unsigned)heads);
         return kipp_launch(head_matvec_kernel<T>, grid, dim3(256), 0, s, 1, (T*)C, (const T*)A, (const T*)W, M, N, K, lda,

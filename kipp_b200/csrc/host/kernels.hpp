@@ -354,29 +354,15 @@ public:
             "head_segments");
     }
     // C[t, h, :] = W_h A[t, h, :] for every head: W_h [N, K] at w + h * w_head, rows of head h at
-    // a + h * a_head + t * lda, results at c + h * c_head + t * ldc.  bfloat16 products of many
-    // tokens whose operands the tensor-core kernel takes run there, head by head; else CUDA cores.
+    // a + h * a_head + t * lda, results at c + h * c_head + t * ldc; one launch for all heads
+    // (head_ops.cu chooses between its kernels by the number of tokens, the type and the alignment).
     void head_matmul(void* c, long long ldc, long long c_head, const void* a, long long lda, long long a_head,
                      const void* w, long long w_head, int dtype, int M, int N, int K, int heads) {
-        const size_t es = dtype_size(dtype);
-        bool tc = dtype == BF16 && M >= HEAD_MATMUL_TC_MIN_TOKENS && K % 8 == 0 && ldc % 8 == 0;
-        for (int h = 0; tc && h < heads; ++h)
-            tc = gemm_tc_ok(dtype, static_cast<const char*>(a) + (size_t)h * a_head * es, lda,
-                            static_cast<const char*>(w) + (size_t)h * w_head * es, K) &&
-                 ((uintptr_t)(static_cast<char*>(c) + (size_t)h * c_head * es) & 15) == 0;
-        if (tc) {
-            for (int h = 0; h < heads; ++h)
-                gemm(static_cast<char*>(c) + (size_t)h * c_head * es, dtype, ldc,
-                     static_cast<const char*>(a) + (size_t)h * a_head * es, lda,
-                     static_cast<const char*>(w) + (size_t)h * w_head * es, K, dtype, M, N, K, EPI_STORE);
-            return;
-        }
         using Fn = int (*)(void*, const void*, const void*, int, int, int, int, int, long long, long long, long long,
                            long long, long long, void*);
         static Fn f = kernel_symbol<Fn>("head_ops", "kipp_head_matmul");
         run(f(c, a, w, dtype, M, N, K, heads, lda, a_head, w_head, ldc, c_head, stream), "head_matmul");
     }
-    static constexpr int HEAD_MATMUL_TC_MIN_TOKENS = 256;
     // out[h] = in[h]^T for `heads` row-major matrices of [rows, cols]
     void transpose_heads(void* out, const void* in, int dtype, int heads, int rows, int cols) {
         using Fn = int (*)(void*, const void*, int, int, int, int, void*);
