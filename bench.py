@@ -162,7 +162,7 @@ def varunex_of(size: str, vocab: int = 32000) -> dict:
                         "rot": {"base": 1e6, "dims": dim // 2}, "scale": (dim + dim // 2) ** -0.5}, "mlp": mlp}
     diff = {"type": "attention",
             "mixer": {"heads": heads, "kv_heads": kv, "dim": dim // 2, "vdim": dim, "diff": 0.5, "mask": {"size": DESIGN_WINDOW},
-                      "rot": {"base": 5e4, "dims": dim // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}},
+                      "rot": {"base": 5e5, "dims": dim // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
                       "scale": (dim // 2) ** -0.5}, "mlp": mlp}
     order = [memory, latent, diff, latent]
     return {"architecture": "Varunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
