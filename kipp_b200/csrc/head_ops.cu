@@ -291,9 +291,9 @@ __global__ void transpose_heads_kernel(T* __restrict__ out, const T* __restrict_
 template <typename T>
 int launch_head_matmul(void* C, const void* A, const void* W, int M, int N, int K, int heads, long long lda,
                        long long a_head, long long w_head, long long ldc, long long c_head, cudaStream_t s) {
-    // the tensor-core kernel: bfloat16, more tokens than the weight-streaming kernel takes, rows of
-    // both operands on 16-byte boundaries, results on 4-byte ones
-    if (sizeof(T) == 2 && M > 2 * MT && K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 && w_head % 8 == 0 && ldc % 2 == 0 &&
+    // the tensor-core kernel: bfloat16 at any number of tokens (a decoded token and a prompt's token
+    // then sum in the same order), rows of both operands on 16-byte boundaries, results on 4-byte ones
+    if (sizeof(T) == 2 && K % 8 == 0 && lda % 8 == 0 && a_head % 8 == 0 && w_head % 8 == 0 && ldc % 2 == 0 &&
         c_head % 2 == 0 && (((uintptr_t)A | (uintptr_t)W) & 15) == 0 && ((uintptr_t)C & 3) == 0) {
         const dim3 grid((unsigned)((N + HN - 1) / HN), (unsigned)((M + HM - 1) / HM), (unsigned)heads);
         if (grid.y > 65535) return KIPP_ERR_ARG;

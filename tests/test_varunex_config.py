@@ -55,7 +55,7 @@ def test_the_mixers_take_their_constants_from_the_configuration():
     assert diff["lambda_init"] == 0.3 and diff["num_kv_heads"] == 2 and diff["position"]["kind"] == "stretched_rotary"
     assert diff["position"]["factor"] == 8.0 and diff["position"]["original"] == 64
     assert plain_diff["window"] == 0 and plain_diff["position"]["kind"] == "rotary"
-    assert memory["gate_cap"] == 15.0 and memory["value_dim"] == 40 and memory["head_dim"] == 16
+    assert memory["gate_cap"] == 10.0 and memory["value_dim"] == 40 and memory["head_dim"] == 16
 
 
 def test_tensor_names_and_shapes():

@@ -44,7 +44,7 @@ CONFIGS = {
     "A": {"architecture": "Varunex", "vocab": 300, "width": 64, "norm": {"eps": 1e-5},
           "layers": [latent_layer(4, 16, 8, 24, 32, 40, 96),
                      diff_layer(4, 2, 16, 24, 20, 8, None, diff=0.3, scaling=(8.0, 1.0, 4.0, 64)),
-                     memory_layer(2, 16, 40, 15.0, 72),
+                     memory_layer(2, 16, 40, 10.0, 72),
                      diff_layer(2, 2, 8, 8, 0, 8, 48, diff=0.6, base=500.0),
                      latent_layer(2, 8, 16, 8, 16, 24, None, base=300.0, scale=0.5),
                      memory_layer(3, 8, 8, 4.0, None)]},
@@ -57,7 +57,7 @@ CONFIGS = {
     # head sizes of 32, 64 and 128, as many key/value heads as heads, a long window, a memory of
     # 64 x 128 per head (several slices of value columns, several threads per column)
     "C": {"architecture": "Varunex", "vocab": 512, "width": 128, "norm": {"eps": 1e-6},
-          "layers": [diff_layer(4, 4, 64, 64, 100, 32, 256, diff=0.2, base=1e6, scaling=(4.0, 1.0, 4.0, 256), scale=0.2),
+          "layers": [diff_layer(4, 4, 64, 64, 100, 32, 256, diff=0.2, base=2e5, scaling=(4.0, 2.0, 8.0, 256), scale=0.2),
                      latent_layer(4, 32, 16, 32, 64, 48, 192, base=1e5),
                      memory_layer(2, 64, 128, 15.0, None),
                      latent_layer(2, 64, 64, 128, 128, 96, 128, base=1e4, scale=0.1)]},
