@@ -15,9 +15,9 @@
 // states its layout as data: keys made of parts, biases, rotation of a head's tail.
 //
 // kipp_head_matmul: out[t, h, :] = W_h a[t, h, :] for every head h, W_h [n, k] row-major, with
-// float32 accumulation, all heads in one launch: few tokens by a kernel that reads the weights
-// once, many tokens in bfloat16 on the tensor cores (mma.sync), the rest in tiles on the CUDA
-// cores.  (Products with a latent: keys absorbed into queries, values expanded after the
+// float32 accumulation, all heads in one launch: in bfloat16 on the tensor cores (mma.sync); in
+// 32-bit, or where rows do not start on 16-byte boundaries, few tokens by a kernel that reads the
+// weights once and more tokens in tiles on the CUDA cores.  (Products with a latent: keys absorbed into queries, values expanded after the
 // weighted sum.)
 #include "common.cuh"
 #include <math.h>
@@ -208,8 +208,7 @@ head_matvec_kernel(T* __restrict__ C, const T* __restrict__ A, const T* __restri
     }
 }
 
-// Many tokens in bfloat16: the same product on the tensor cores (mma.sync m16n8k16), all heads in one
-// launch.  A block of 4 warps takes 64 tokens x 64 features of one head; K is walked in steps of 32
+// In bfloat16: the same product on the tensor cores (mma.sync m16n8k16), all heads in one launch.  A block of 4 warps takes 64 tokens x 64 features of one head; K is walked in steps of 32
 // through shared memory (16-byte asynchronous copies, zeros beyond M, N and K); a warp owns 16
 // tokens x 64 features.  The sum over k runs in the same order for every token.
 constexpr int HM = 64, HN = 64, HK = 32, HLD = HK + 8;
