@@ -74,9 +74,15 @@ CONFIGS = {
                      latent_layer(3, 6, 4, 5, 12, 10, 36, scale=0.8),
                      memory_layer(1, 12, 7, 9.0, None),
                      latent_layer(5, 8, 8, 8, 24, 20, 30)]},
+    # more heads than one block of the tensor-core kernels holds: 20 heads on one latent (two groups
+    # of 16 rows, the second partly empty), 40 score maps on 5 key/value heads (dealt out to blocks)
+    "F": {"architecture": "Varunex", "vocab": 120, "width": 64, "norm": {"eps": 1e-5},
+          "layers": [latent_layer(20, 8, 8, 8, 24, 16, 64),
+                     diff_layer(20, 5, 16, 16, 50, 8, None, diff=0.25)]},
 }
 INIT = {"A": dict(seed=3, sigma=0.15, norm_jitter=0.2), "B": dict(seed=5, sigma=0.2, norm_jitter=0.1),
-        "C": dict(seed=9, sigma=0.08, norm_jitter=0.15), "D": dict(seed=12, sigma=0.2, norm_jitter=0.1), "E": dict(seed=15, sigma=0.2, norm_jitter=0.1)}
+        "C": dict(seed=9, sigma=0.08, norm_jitter=0.15), "D": dict(seed=12, sigma=0.2, norm_jitter=0.1), "E": dict(seed=15, sigma=0.2, norm_jitter=0.1),
+        "F": dict(seed=17, sigma=0.15, norm_jitter=0.1)}
 
 _tmp = tempfile.TemporaryDirectory(prefix="kipp_b200_varunex_")
 
