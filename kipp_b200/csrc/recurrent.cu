@@ -31,8 +31,8 @@
 // Three kernels per step.  (1) prepare: a warp per (token, head) forms the token's vectors in
 // float32 (q/r, k, and for the delta rule w, a * u, u) in a workspace; fully parallel over the
 // step's tokens.  (2) scan: a block per (entry, head, slice of 32 value columns) -- the columns
-// of S evolve independently -- walks the entry's tokens in order; a thread owns one column and a
-// run of at most 32 key rows in registers (P = 1, 2, 4, 8 or 16 threads per column, neighbours in a
+// of S evolve independently -- walks the entry's tokens in order; a thread owns one column and
+// at most 32 key rows of it (every P-th row) in registers (P = 1, 2, 4, 8 or 16 threads per column, neighbours in a
 // warp, their partial sums met by shuffles); the token vectors come through shared memory in
 // batches.  The state is read from and written back to its slot once per launch; a decoded token
 // is a batch of one.  (3) finish: a warp per (token, head) divides by the root mean square,
@@ -197,7 +197,8 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     const int e = eh / a.heads, h = eh % a.heads;
     const int row0 = a.q_start[e], n_tok = a.q_start[e + 1] - row0;
     const int p = tid % P, cl = tid / P, col = slice * VS + cl;
-    const int d0 = p * CHUNK;
+    // the key rows of a column are dealt out to its P threads in turn (thread p has rows p, p + P, ...): the
+    // threads of a column then read neighbouring words of a token's vectors, which no bank serves twice
     const bool live = col < V;
     float* slot_base = a.state + (size_t)a.slots[e] * (size_t)(a.slot_stride > 0 ? a.slot_stride : (long long)a.heads * D * V);
     float* S_slot = slot_base + (size_t)h * D * V;
@@ -210,7 +211,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
 
     float S[CHUNK];
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) S[i] = (live && d0 + i < D) ? S_slot[(size_t)(d0 + i) * V + col] : 0.f;
+    for (int i = 0; i < CHUNK; ++i) S[i] = (live && p + P * i < D) ? S_slot[(size_t)(p + P * i) * V + col] : 0.f;
     const float decay = DELTA ? 0.f : a.decay[h];
 
     load_batch(smem, smem + TB * nvd, recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
@@ -228,7 +229,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
         const float* vvb = tvb + TB * nvd;
         for (int tt = 0; tt < nb; ++tt) {
             const float v = vvb[tt * VS + cl];
-            const float* base = tvb + tt * nvd + d0;
+            const float* base = tvb + tt * nvd + p;
             float us = 0.f, keep = 0.f, take = 0.f;
             if (KIND == GATED_MEMORY) {
                 const float gi = tvb[tt * nvd + NV * D], gf = tvb[tt * nvd + NV * D + 1];
@@ -240,20 +241,20 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
             if (DELTA) {
 #pragma unroll
                 for (int i = 0; i < CHUNK; ++i)
-                    if (d0 + i < D) us = fmaf(base[4 * D + i], S[i], us);
+                    if (p + P * i < D) us = fmaf(base[4 * D + P * i], S[i], us);
 #pragma unroll
                 for (int x = P / 2; x > 0; x >>= 1) us += __shfl_xor_sync(0xffffffffu, us, x);
             }
             float o = 0.f;
 #pragma unroll
             for (int i = 0; i < CHUNK; ++i) {
-                if (d0 + i < D) {
+                if (p + P * i < D) {
                     float s;
-                    if (DELTA) s = fmaf(base[D + i], v, fmaf(-base[3 * D + i], us, base[2 * D + i] * S[i]));
-                    else if (KIND == GATED_MEMORY) s = fmaf(take * base[D + i], v, keep * S[i]);
-                    else s = fmaf(base[D + i], v, decay * S[i]);
+                    if (DELTA) s = fmaf(base[D + P * i], v, fmaf(-base[3 * D + P * i], us, base[2 * D + P * i] * S[i]));
+                    else if (KIND == GATED_MEMORY) s = fmaf(take * base[D + P * i], v, keep * S[i]);
+                    else s = fmaf(base[D + P * i], v, decay * S[i]);
                     S[i] = s;
-                    o = fmaf(s, base[i], o);
+                    o = fmaf(s, base[P * i], o);
                 }
             }
 #pragma unroll
@@ -265,7 +266,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     }
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i)
-        if (live && d0 + i < D) S_slot[(size_t)(d0 + i) * V + col] = S[i];
+        if (live && p + P * i < D) S_slot[(size_t)(p + P * i) * V + col] = S[i];
     if (KIND == GATED_MEMORY && tid == 0) *m_slot = m_run;
 }
 
