@@ -246,12 +246,13 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                 for (int x = P / 2; x > 0; x >>= 1) us += __shfl_xor_sync(0xffffffffu, us, x);
             }
             float o = 0.f;
+            const float tv = take * v;                  // (gated memory: the input gate's weight on this column's value)
 #pragma unroll
             for (int i = 0; i < CHUNK; ++i) {
                 if (p + P * i < D) {
                     float s;
                     if (DELTA) s = fmaf(base[D + P * i], v, fmaf(-base[3 * D + P * i], us, base[2 * D + P * i] * S[i]));
-                    else if (KIND == GATED_MEMORY) s = fmaf(take * base[D + P * i], v, keep * S[i]);
+                    else if (KIND == GATED_MEMORY) s = fmaf(base[D + P * i], tv, keep * S[i]);
                     else s = fmaf(base[D + P * i], v, decay * S[i]);
                     S[i] = s;
                     o = fmaf(s, base[P * i], o);
@@ -322,9 +323,10 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     const int D = a.dim, V = a.v_dim + Rec<DELTA>::XV;
     constexpr int NV = Rec<DELTA>::NV, XG = Rec<DELTA>::XG;
     // threads per column: runs of 8 key rows where the head allows (short chains of dependent
-    // multiply-adds, more warps per block), at most 16 threads
+    // multiply-adds, more warps per block), at most 8 threads (16 only where a head has more than 256 key rows)
     int P = 1;
-    while (P < 16 && (D + P - 1) / P > 8) P *= 2;
+    while (P < 8 && (D + P - 1) / P > 8) P *= 2;
+    if ((D + P - 1) / P > MAX_CHUNK) P = 16;
     if ((D + P - 1) / P > MAX_CHUNK || scratch == nullptr) return KIPP_ERR_ARG;
     const size_t per_token = ((size_t)NV * D + XG + VS) * sizeof(float);
     int batch = (int)std::min<size_t>(32, (20 * 1024) / per_token);       // two buffers of at most 20 KB
