@@ -177,7 +177,9 @@ __device__ __forceinline__ void load_batch(float* __restrict__ tv, float* __rest
     cp_async_commit();
 }
 
-template <typename T, int KIND, int P, int CHUNK>
+// VEC: the head's key size is a multiple of 4: a thread's rows come in groups of four neighbours
+// (rows 4 (p + P g) .. + 3), read with one 16-byte load per vector.
+template <typename T, int KIND, int P, int CHUNK, bool VEC>
 __global__ void __launch_bounds__(VS * P)
 recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __restrict__ o_raw, int v_slices,
                       int tokens) {
@@ -197,8 +199,10 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     const int e = eh / a.heads, h = eh % a.heads;
     const int row0 = a.q_start[e], n_tok = a.q_start[e + 1] - row0;
     const int p = tid % P, cl = tid / P, col = slice * VS + cl;
-    // the key rows of a column are dealt out to its P threads in turn (thread p has rows p, p + P, ...): the
-    // threads of a column then read neighbouring words of a token's vectors, which no bank serves twice
+    // the key rows of a column are dealt out to its P threads in turn (thread p has rows p, p + P, ..., or
+    // groups of four rows in turn): the threads of a column then read neighbouring words of a token's
+    // vectors, which no bank serves twice
+    auto row_of = [p](int i) { return VEC ? 4 * (p + P * (i >> 2)) + (i & 3) : p + P * i; };
     const bool live = col < V;
     float* slot_base = a.state + (size_t)a.slots[e] * (size_t)(a.slot_stride > 0 ? a.slot_stride : (long long)a.heads * D * V);
     float* S_slot = slot_base + (size_t)h * D * V;
@@ -211,7 +215,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
 
     float S[CHUNK];
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) S[i] = (live && p + P * i < D) ? S_slot[(size_t)(p + P * i) * V + col] : 0.f;
+    for (int i = 0; i < CHUNK; ++i) S[i] = (live && row_of(i) < D) ? S_slot[(size_t)row_of(i) * V + col] : 0.f;
     const float decay = DELTA ? 0.f : a.decay[h];
 
     load_batch(smem, smem + TB * nvd, recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
@@ -238,24 +242,62 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                 take = expf(gi - m_new);
                 m_run = m_new;
             }
+            const float* tok = tvb + tt * nvd;
             if (DELTA) {
+                if (VEC) {
 #pragma unroll
-                for (int i = 0; i < CHUNK; ++i)
-                    if (p + P * i < D) us = fmaf(base[4 * D + P * i], S[i], us);
+                    for (int g = 0; g < CHUNK / 4; ++g) {
+                        const int r = 4 * (p + P * g);
+                        if (r < D) {
+                            const float4 u4 = *reinterpret_cast<const float4*>(tok + 4 * D + r);
+                            us = fmaf(u4.x, S[4 * g], us); us = fmaf(u4.y, S[4 * g + 1], us);
+                            us = fmaf(u4.z, S[4 * g + 2], us); us = fmaf(u4.w, S[4 * g + 3], us);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < CHUNK; ++i)
+                        if (p + P * i < D) us = fmaf(base[4 * D + P * i], S[i], us);
+                }
 #pragma unroll
                 for (int x = P / 2; x > 0; x >>= 1) us += __shfl_xor_sync(0xffffffffu, us, x);
             }
             float o = 0.f;
             const float tv = take * v;                  // (gated memory: the input gate's weight on this column's value)
+            if (VEC) {
 #pragma unroll
-            for (int i = 0; i < CHUNK; ++i) {
-                if (p + P * i < D) {
-                    float s;
-                    if (DELTA) s = fmaf(base[D + P * i], v, fmaf(-base[3 * D + P * i], us, base[2 * D + P * i] * S[i]));
-                    else if (KIND == GATED_MEMORY) s = fmaf(base[D + P * i], tv, keep * S[i]);
-                    else s = fmaf(base[D + P * i], v, decay * S[i]);
-                    S[i] = s;
-                    o = fmaf(s, base[P * i], o);
+                for (int g = 0; g < CHUNK / 4; ++g) {
+                    const int r = 4 * (p + P * g);
+                    if (r < D) {
+                        float qq[4], kk[4], ww[4], aa[4];
+                        *reinterpret_cast<float4*>(qq) = *reinterpret_cast<const float4*>(tok + r);
+                        *reinterpret_cast<float4*>(kk) = *reinterpret_cast<const float4*>(tok + D + r);
+                        if (DELTA) {
+                            *reinterpret_cast<float4*>(ww) = *reinterpret_cast<const float4*>(tok + 2 * D + r);
+                            *reinterpret_cast<float4*>(aa) = *reinterpret_cast<const float4*>(tok + 3 * D + r);
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float s;
+                            if (DELTA) s = fmaf(kk[j], v, fmaf(-aa[j], us, ww[j] * S[4 * g + j]));
+                            else if (KIND == GATED_MEMORY) s = fmaf(kk[j], tv, keep * S[4 * g + j]);
+                            else s = fmaf(kk[j], v, decay * S[4 * g + j]);
+                            S[4 * g + j] = s;
+                            o = fmaf(s, qq[j], o);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < CHUNK; ++i) {
+                    if (p + P * i < D) {
+                        float s;
+                        if (DELTA) s = fmaf(base[D + P * i], v, fmaf(-base[3 * D + P * i], us, base[2 * D + P * i] * S[i]));
+                        else if (KIND == GATED_MEMORY) s = fmaf(base[D + P * i], tv, keep * S[i]);
+                        else s = fmaf(base[D + P * i], v, decay * S[i]);
+                        S[i] = s;
+                        o = fmaf(s, base[P * i], o);
+                    }
                 }
             }
 #pragma unroll
@@ -267,7 +309,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     }
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i)
-        if (live && p + P * i < D) S_slot[(size_t)(p + P * i) * V + col] = S[i];
+        if (live && row_of(i) < D) S_slot[(size_t)row_of(i) * V + col] = S[i];
     if (KIND == GATED_MEMORY && tid == 0) *m_slot = m_run;
 }
 
@@ -307,14 +349,22 @@ recurrent_finish_kernel(const ScanArgs a, const float* __restrict__ o_raw, int t
     }
 }
 
+template <typename T, int DELTA, int P, bool VEC>
+int launch_scan_rows(const ScanArgs& b, const float* vec, float* o_raw, int slices, int tokens, dim3 grid, size_t smem,
+                     cudaStream_t stream) {
+    const int chunk = (b.dim + P - 1) / P;
+    if (chunk <= 8) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 8, VEC>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+    if (chunk <= 16) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 16, VEC>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+    if (chunk <= 24) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 24, VEC>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+    return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 32, VEC>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+}
 template <typename T, int DELTA, int P>
 int launch_scan_chunk(const ScanArgs& b, const float* vec, float* o_raw, int slices, int tokens, dim3 grid, size_t smem,
                       cudaStream_t stream) {
-    const int chunk = (b.dim + P - 1) / P;
-    if (chunk <= 8) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 8>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
-    if (chunk <= 16) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 16>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
-    if (chunk <= 24) return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 24>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
-    return kipp_launch(recurrent_scan_kernel<T, DELTA, P, 32>, grid, dim3(VS * P), smem, stream, 1, b, vec, o_raw, slices, tokens);
+    // groups of four rows per 16-byte load where the key size allows (every vector of a record then
+    // starts on a 16-byte boundary)
+    return b.dim % 4 == 0 ? launch_scan_rows<T, DELTA, P, true>(b, vec, o_raw, slices, tokens, grid, smem, stream)
+                          : launch_scan_rows<T, DELTA, P, false>(b, vec, o_raw, slices, tokens, grid, smem, stream);
 }
 
 // scratch: float32 [heads][tokens][NV * dim + v_dim] for the records, then [tokens][heads * v_dim] for raw o
